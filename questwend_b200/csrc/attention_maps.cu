@@ -1,0 +1,560 @@
+// Attention over the paged cache with one or two score maps per head, soft-capped scores and a causal or chunked mask.
+//
+// A query head has `maps` (1 or 2) query vectors of `dim` values, laid out one after the other, and so has a key head;
+// map m of query head h is scored against map m of key head h / (H / G).  Each map is a softmax attention of its own
+// over the SAME values (size vdim).  With two maps the head's output is their difference, a1 - lambda * a2 (differential
+// attention; lambda is one number for the layer); with `norm_out` the output is then divided by its root mean square
+// over vdim (eps inside the root) and multiplied by out_scale.
+//   score = q . k * scale;  softcap > 0:  score <- softcap * tanh(score / softcap)
+//   mask:  key j is seen from position p when j <= p and (chunk > 0) floor(j / chunk) = floor(p / chunk); chunks are
+//          counted from position 0 of the sequence.
+// Scores, maxima, sums, accumulators, the difference and the norm are 32-bit; q and the cache are float or bfloat16.
+// The cache: K pool [pages, G, 64, maps * dim], V pool [pages, G, 64, vdim].
+//
+//   maps_prep         bias, per-map RMS norm of q and k (a weight of dim values shared by heads and maps), rotation of the
+//                     first rdims values of every map of q and k, cache write of a step's tokens; q out
+//   maps_prefill      any number of new tokens per sequence (float and bfloat16, any sizes that are multiples of 8)
+//   maps_prefill_mma  bfloat16 prompts on the tensor cores
+//   maps_decode       one new token per sequence: runs of pages, one block of threads a run, then maps_merge, which also
+//                     takes the difference and the norm
+#include "common.cuh"
+
+#define QWB_MAPS_MAX_DIM 256
+#define QWB_MAPS_PAGE 64
+#define QWB_MAPS_MAX 2
+#define QWB_MAPS_ROWS 8           // (query head, map) pairs per block of the decode kernel
+#define QWB_MAPS_RUN_PAGES 2      // pages per run of the decode kernel, doubled while a sequence would have more than ...
+#define QWB_MAPS_MAX_RUNS 16      // ... this many runs: follows from the sequence's own length, not from the batch
+
+// value i of a vector after its first n values were turned by the angle whose cos and sin are cs[m], sn[m] for pair m
+__device__ __forceinline__ float maps_turned(const float* v, int i, int n, const float* cs, const float* sn, int interleaved) {
+    if (i >= n) return v[i];
+    const int half = n >> 1;
+    int m, first;
+    float a, b;
+    if (interleaved) { m = i >> 1; first = !(i & 1); a = v[2 * m]; b = v[2 * m + 1]; }
+    else { m = i < half ? i : i - half; first = i < half; a = v[m]; b = v[m + half]; }
+    const float c = cs[m], s = sn[m];
+    return first ? a * c - b * s : b * c + a * s;
+}
+
+__device__ __forceinline__ int maps_first_key(int p, int chunk) { return chunk > 0 ? (p / chunk) * chunk : 0; }
+
+__device__ __forceinline__ float maps_cap(float s, float cap, float inv_cap) { return cap > 0.f ? cap * tanhf(s * inv_cap) : s; }
+
+// ---------------------------------------------------------------------------------
+// prep: grid (T, ceil(items / 4)), 4 warps, a warp per (token, item); items = H * maps query maps, G * maps key maps,
+// G values.  qkv [T, (H + G) * maps * dim + G * vdim] float: the projections (after a convolution, if the mixer has one).
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void maps_prep_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, const float* __restrict__ qw,
+                                 const float* __restrict__ kw, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                 const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int* __restrict__ page_table,
+                                 int table_width, T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool, int H, int G,
+                                 int maps, int dim, int vdim, int rdims, int interleaved, float eps, int store_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float bufs[4][QWB_MAPS_MAX_DIM];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.y * 4 + warp, t = blockIdx.x;
+    const int nq = H * maps, nk = G * maps;
+    if (item >= nq + nk + G) return;
+    float* buf = bufs[warp];
+    const int ld = (nq + nk) * dim + G * vdim;
+    const bool is_q = item < nq, is_k = !is_q && item < nq + nk;
+    const int n = (is_q || is_k) ? dim : vdim;
+    const int col = is_q ? item * dim : (is_k ? nq * dim + (item - nq) * dim : (nq + nk) * dim + (item - nq - nk) * vdim);
+    const float* src = qkv + (size_t)t * ld + col;
+    float ss = 0.f;
+    for (int i = lane; i < n; i += 32) { const float v = src[i] + (bias ? bias[col + i] : 0.f); buf[i] = v; ss += v * v; }
+    const float* w = is_q ? qw : (is_k ? kw : nullptr);
+    if (w) {
+        const float scale = rsqrtf(warp_sum(ss) / (float)n + eps);
+        for (int i = lane; i < n; i += 32) buf[i] = buf[i] * scale * w[i];
+    }
+    __syncwarp();
+    const int rd = (is_q || is_k) ? rdims : 0;
+    const float* cs = cos_t + (size_t)t * (rd >> 1);
+    const float* sn = sin_t + (size_t)t * (rd >> 1);
+    T* dst;
+    if (is_q) dst = q_out + (size_t)t * nq * dim + (size_t)item * dim;
+    else {
+        if (!store_kv) return;
+        const int b = tok_seq[t], p = tok_pos[t];
+        const size_t page = page_table[(size_t)b * table_width + p / QWB_MAPS_PAGE];
+        if (is_k) {
+            const int head = (item - nq) / maps, m = (item - nq) % maps;
+            dst = k_pool + ((page * G + head) * QWB_MAPS_PAGE + p % QWB_MAPS_PAGE) * (size_t)(maps * dim) + m * dim;
+        } else {
+            dst = v_pool + ((page * G + (item - nq - nk)) * QWB_MAPS_PAGE + p % QWB_MAPS_PAGE) * (size_t)vdim;
+        }
+    }
+    for (int i = lane; i < n; i += 32) dst[i] = from_f32<T>(rd > 0 ? maps_turned(buf, i, rd, cs, sn, interleaved) : buf[i]);
+}
+
+static int check_maps_sizes(const char* what, int H, int G, int maps, int dim, int vdim, int table_width, int chunk) {
+    if (H <= 0 || G <= 0 || H % G) return qwb_fail(QWB_ERR_ARG, "%s: %d query heads are not a multiple of %d key/value heads", what, H, G);
+    if (maps < 1 || maps > QWB_MAPS_MAX) return qwb_fail(QWB_ERR_ARG, "%s: %d score maps per head (1 or 2)", what, maps);
+    if (dim <= 0 || dim % 8 || dim > QWB_MAPS_MAX_DIM || vdim <= 0 || vdim % 8 || vdim > QWB_MAPS_MAX_DIM)
+        return qwb_fail(QWB_ERR_ARG, "%s: key size %d or value size %d is not a multiple of 8 in [8, %d]", what, dim, vdim, QWB_MAPS_MAX_DIM);
+    if (table_width <= 0 || chunk < 0) return qwb_fail(QWB_ERR_ARG, "%s: bad table width %d or chunk %d", what, table_width, chunk);
+    return 0;
+}
+
+extern "C" int qwb_maps_prep(const float* qkv, const float* bias, const float* qw, const float* kw, const float* cos_t, const float* sin_t,
+                             const int* tok_seq, const int* tok_pos, const int* page_table, int table_width, void* q_out, void* k_pool,
+                             void* v_pool, int dtype, int T, int H, int G, int maps, int dim, int vdim, int rdims, int interleaved,
+                             float eps, int store_kv, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (int rc = check_maps_sizes("maps_prep", H, G, maps, dim, vdim, table_width, 0)) return rc;
+    if (rdims < 0 || rdims > dim || rdims % 2) return qwb_fail(QWB_ERR_ARG, "maps_prep: a rotation of %d of %d values", rdims, dim);
+    if (rdims > 0 && (!cos_t || !sin_t)) return qwb_fail(QWB_ERR_ARG, "maps_prep: a rotation without its table");
+    dim3 grid(T, ((H + G) * maps + G + 3) / 4);
+    if (dtype == QWB_DT_F32)
+        qwb_launch(maps_prep_kernel<float>, grid, 128, 0, stream, qkv, bias, qw, kw, cos_t, sin_t, tok_seq, tok_pos, page_table, table_width,
+                   (float*)q_out, (float*)k_pool, (float*)v_pool, H, G, maps, dim, vdim, rdims, interleaved, eps, store_kv);
+    else if (dtype == QWB_DT_BF16)
+        qwb_launch(maps_prep_kernel<bf16>, grid, 128, 0, stream, qkv, bias, qw, kw, cos_t, sin_t, tok_seq, tok_pos, page_table, table_width,
+                   (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, H, G, maps, dim, vdim, rdims, interleaved, eps, store_kv);
+    else return qwb_fail(QWB_ERR_ARG, "maps_prep: unknown dtype %d", dtype);
+    return qwb_check_launch("maps_prep");
+}
+
+// ---------------------------------------------------------------------------------
+// prefill: one block per (tile of 16 queries, query head, sequence); 4 warps, each owns 4 queries; keys come in tiles of
+// 32 (one key per lane), from the first key that the tile's first query sees to the tile's last query; the maps one
+// after the other over the same tiles.
+// ---------------------------------------------------------------------------------
+template <typename T, int NC>   // NC = ceil(vdim / 32) rounded up to 2, 4 or 8
+__global__ void maps_prefill_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                                    const int* __restrict__ page_table, const int* __restrict__ cu_seqlens, const int* __restrict__ pos0,
+                                    T* __restrict__ out, int H, int G, int maps, int dim, int vdim, int table_width, float scale,
+                                    float softcap, int chunk, float lambda, int norm_out, float eps, float out_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int BQ = 16, BK = 32, QPW = 4, PG = QWB_MAPS_PAGE;
+    extern __shared__ float smem[];
+    float* Qs = smem;                         // [BQ][dim], already scaled
+    float* Ks = Qs + BQ * dim;                // [BK][dim + 1]
+    float* Vs = Ks + BK * (dim + 1);          // [BK][vdim]
+
+    const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BQ;
+    const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
+    if (q0 >= n_new) return;
+    const int g = h / (H / G);
+    const int p0 = pos0[b];
+    const int nq = min(BQ, n_new - q0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kdim = maps * dim;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+
+    float res[QPW][NC];                       // map 0's normed sums, then the difference
+    const int k_last = p0 + q0 + nq - 1;
+    const int k_first = maps_first_key(p0 + q0, chunk);
+    const int* pages = page_table + (size_t)b * table_width;
+
+    for (int mp = 0; mp < maps; ++mp) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < BQ * dim; idx += blockDim.x) {
+            const int i = idx / dim, d = idx - i * dim;
+            Qs[idx] = i < nq ? to_f32(q[((size_t)(t0 + q0 + i) * H + h) * kdim + mp * dim + d]) * scale : 0.f;
+        }
+        float m[QPW], l[QPW], acc[QPW][NC];
+#pragma unroll
+        for (int i = 0; i < QPW; ++i) {
+            m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
+        }
+        for (int kt = (k_first / BK) * BK; kt <= k_last; kt += BK) {
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < BK * dim; idx += blockDim.x) {
+                const int j = idx / dim, d = idx - j * dim, key = kt + j;
+                Ks[j * (dim + 1) + d] = key <= k_last ? to_f32(k_pool[(((size_t)pages[key / PG] * G + g) * PG + key % PG) * kdim + mp * dim + d]) : 0.f;
+            }
+            for (int idx = threadIdx.x; idx < BK * vdim; idx += blockDim.x) {
+                const int j = idx / vdim, d = idx - j * vdim, key = kt + j;
+                Vs[idx] = key <= k_last ? to_f32(v_pool[(((size_t)pages[key / PG] * G + g) * PG + key % PG) * vdim + d]) : 0.f;
+            }
+            __syncthreads();
+
+            float s[QPW];
+#pragma unroll
+            for (int i = 0; i < QPW; ++i) s[i] = 0.f;
+            const float* krow = Ks + lane * (dim + 1);
+            for (int d = 0; d < dim; ++d) {
+                const float kd = krow[d];
+#pragma unroll
+                for (int i = 0; i < QPW; ++i) s[i] += Qs[(warp * QPW + i) * dim + d] * kd;
+            }
+            const int key = kt + lane;
+            float p[QPW];
+#pragma unroll
+            for (int i = 0; i < QPW; ++i) {
+                const int qi = warp * QPW + i;
+                const int qp = p0 + q0 + qi;
+                const bool ok = qi < nq && key <= qp && key >= maps_first_key(qp, chunk);
+                const float si = ok ? maps_cap(s[i], softcap, inv_cap) : -INFINITY;
+                const float m_new = fmaxf(m[i], warp_max(si));
+                if (m_new == -INFINITY) { p[i] = 0.f; continue; }       // nothing visible so far (whole warp agrees)
+                const float alpha = expf(m[i] - m_new);                 // m = -inf gives 0
+                p[i] = ok ? expf(si - m_new) : 0.f;
+                l[i] = l[i] * alpha + warp_sum(p[i]);
+                m[i] = m_new;
+#pragma unroll
+                for (int c = 0; c < NC; ++c) acc[i][c] *= alpha;
+            }
+            for (int j = 0; j < BK; ++j) {
+                float pj[QPW];
+#pragma unroll
+                for (int i = 0; i < QPW; ++i) pj[i] = __shfl_sync(0xffffffffu, p[i], j);
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    const int d = lane + 32 * c;
+                    if (d < vdim) {
+                        const float v = Vs[j * vdim + d];
+#pragma unroll
+                        for (int i = 0; i < QPW; ++i) acc[i][c] += pj[i] * v;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < QPW; ++i) {
+            const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const float a = acc[i][c] * inv;
+                res[i][c] = mp == 0 ? a : res[i][c] - lambda * a;
+            }
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < QPW; ++i) {
+        const int qi = warp * QPW + i;
+        float mul = 1.f;
+        if (norm_out) {
+            float ss = 0.f;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) if (lane + 32 * c < vdim) ss += res[i][c] * res[i][c];
+            mul = rsqrtf(warp_sum(ss) / (float)vdim + eps) * out_scale;
+        }
+        if (qi >= nq) continue;
+        T* o = out + ((size_t)(t0 + q0 + qi) * H + h) * vdim;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const int d = lane + 32 * c;
+            if (d < vdim) o[d] = from_f32<T>(res[i][c] * mul);
+        }
+    }
+}
+
+template <typename T>
+static int launch_maps_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
+                               const int* pos0, void* out, int B, int max_new, int H, int G, int maps, int dim, int vdim, int table_width,
+                               float scale, float softcap, int chunk, float lambda, int norm_out, float eps, float out_scale,
+                               cudaStream_t stream) {
+    const size_t smem = ((size_t)16 * dim + 32 * (dim + 1) + 32 * vdim) * sizeof(float);
+    dim3 grid((max_new + 15) / 16, H, B);
+    const int nc = (vdim + 31) / 32;
+#define QWB_LAUNCH_MAPS_PREFILL(NC)                                                                              \
+    do {                                                                                                         \
+        if (smem > 48 * 1024) {                                                                                  \
+            cudaError_t e = cudaFuncSetAttribute(maps_prefill_kernel<T, NC>,                                     \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+            if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "maps_prefill: %s", cudaGetErrorString(e));      \
+        }                                                                                                        \
+        qwb_launch(maps_prefill_kernel<T, NC>, grid, 128, smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool, \
+            page_table, cu_seqlens, pos0, (T*)out, H, G, maps, dim, vdim, table_width, scale, softcap, chunk, lambda, norm_out, \
+            eps, out_scale);                                                                                     \
+    } while (0)
+    if (nc <= 2) QWB_LAUNCH_MAPS_PREFILL(2);
+    else if (nc <= 4) QWB_LAUNCH_MAPS_PREFILL(4);
+    else QWB_LAUNCH_MAPS_PREFILL(8);
+#undef QWB_LAUNCH_MAPS_PREFILL
+    return qwb_check_launch("maps_prefill");
+}
+
+// q [T, H, maps * dim]; out [T, H * vdim].
+extern "C" int qwb_maps_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
+                                const int* pos0, void* out, int dtype, int B, int max_new, int H, int G, int maps, int dim, int vdim,
+                                int table_width, float scale, float softcap, int chunk, float lambda, int norm_out, float eps,
+                                float out_scale, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    if (int rc = check_maps_sizes("maps_prefill", H, G, maps, dim, vdim, table_width, chunk)) return rc;
+    if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "maps_prefill: batch %d or heads %d above 65535", B, H);
+    if (dtype == QWB_DT_F32)
+        return launch_maps_prefill<float>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, H, G, maps, dim, vdim, table_width,
+                                          scale, softcap, chunk, lambda, norm_out, eps, out_scale, stream);
+    if (dtype == QWB_DT_BF16)
+        return launch_maps_prefill<bf16>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, H, G, maps, dim, vdim, table_width,
+                                         scale, softcap, chunk, lambda, norm_out, eps, out_scale, stream);
+    return qwb_fail(QWB_ERR_ARG, "maps_prefill: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------
+// decode: one new token per sequence (its position is len - 1).  The keys it sees, first .. len - 1 with first the start
+// of its chunk (or 0), are cut into runs of whole pages counted from the page of the first key: 2 pages a run, doubled
+// while that would give more than 16 runs.  Which keys a run holds follows from the sequence's own length alone.
+// Block = (run, key/value head and slice of its rows, sequence), 128 threads; a row is a (query head, map) pair, up to 8 a
+// block: a page's K and V tiles go to shared memory; thread (key, half of the rows) forms the scores; a warp per row
+// updates maximum and sum; thread d accumulates p v for all rows.
+// ---------------------------------------------------------------------------------
+__device__ __host__ __forceinline__ int maps_run_pages(int first_key, int len) {
+    const int span = (len - 1) / QWB_MAPS_PAGE - first_key / QWB_MAPS_PAGE + 1;
+    int rp = QWB_MAPS_RUN_PAGES;
+    while (span > rp * QWB_MAPS_MAX_RUNS) rp *= 2;
+    return rp;
+}
+
+__device__ __forceinline__ void maps_cp16(void* dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+}
+
+template <typename T>
+__global__ void maps_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                                   const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
+                                   float* __restrict__ part_m, float* __restrict__ part_l, int H, int G, int maps, int dim, int vdim,
+                                   int table_width, float scale, float softcap, int chunk, int n_runs) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int RT = QWB_MAPS_ROWS, VEC = Vec16<T>::N, PG = QWB_MAPS_PAGE;
+    const int b = blockIdx.z, run = blockIdx.x;
+    const int len = seq_len[b];
+    const int first = maps_first_key(len - 1, chunk);
+    const int rp = maps_run_pages(first, len);
+    const int page_lo = first / PG;
+    const int row_first = max(first, (page_lo + run * rp) * PG);
+    const int row_end = min(len, (page_lo + (run + 1) * rp) * PG);
+    if (row_first >= row_end) return;
+
+    const int QG = H / G, rows_g = QG * maps, slices = (rows_g + RT - 1) / RT;
+    const int g = blockIdx.y / slices, r0 = (blockIdx.y % slices) * RT;       // rows of this key/value head: head-in-group * maps + map
+    const int rcount = min(RT, rows_g - r0);
+    const int kdim = maps * dim;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int kld = kdim + VEC;                         // a key row and 16 bytes: rows start in different banks
+    T* Kt = reinterpret_cast<T*>(smem_raw);             // [PG][kdim + VEC]
+    T* Vt = Kt + (size_t)PG * kld;                      // [PG][vdim]
+    float* qs = reinterpret_cast<float*>(Vt + (size_t)PG * vdim);   // [RT][dim], scaled
+    float* sc = qs + RT * dim;                          // [RT][PG]
+    float* m_s = sc + RT * PG;                          // [RT]
+    float* l_s = m_s + RT;
+    float* a_s = l_s + RT;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // row r0 + ri of head g: query head g * QG + (r0 + ri) / maps, map (r0 + ri) % maps; q is [B, H, maps * dim], so the
+    // rows of a key/value head lie one after the other
+    const T* qrow = q + ((size_t)b * H + (size_t)g * QG) * kdim + (size_t)r0 * dim;
+    for (int idx = tid; idx < RT * dim; idx += blockDim.x) {
+        const int ri = idx / dim;
+        qs[idx] = ri < rcount ? to_f32(qrow[idx]) * scale : 0.f;
+    }
+    if (tid < RT) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; a_s[tid] = 1.f; }
+
+    float acc[RT][2];
+#pragma unroll
+    for (int ri = 0; ri < RT; ++ri) acc[ri][0] = acc[ri][1] = 0.f;
+
+    const int* pages = page_table + (size_t)b * table_width;
+    const int my_key = tid % PG, my_slice = tid / PG;                 // two threads a key; each takes every second row
+    const int nchunk = kdim / VEC, dchunk = dim / VEC;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+
+    for (int base = (row_first / PG) * PG; base < row_end; base += PG) {
+        const int n_keys = min(PG, row_end - base);
+        const size_t tile = (size_t)pages[base / PG] * G + g;
+        __syncthreads();                                              // the last page's tiles are no longer read
+        {
+            const uint4* ksrc = reinterpret_cast<const uint4*>(k_pool + tile * PG * kdim);
+            const uint4* vsrc = reinterpret_cast<const uint4*>(v_pool + tile * PG * vdim);
+            uint4* kdst = reinterpret_cast<uint4*>(Kt);
+            uint4* vdst = reinterpret_cast<uint4*>(Vt);
+            for (int i = tid; i < n_keys * nchunk; i += blockDim.x) maps_cp16(kdst + i + i / nchunk, ksrc + i);     // row r starts at r * (nchunk + 1)
+            for (int i = tid; i < n_keys * vdim / VEC; i += blockDim.x) maps_cp16(vdst + i, vsrc + i);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+
+        if (my_key < n_keys) {
+            const Vec16<T>* krow = reinterpret_cast<const Vec16<T>*>(Kt + (size_t)my_key * kld);
+            const bool ok = base + my_key >= row_first;
+#pragma unroll
+            for (int k = 0; k < RT / 2; ++k) {
+                const int ri = my_slice + 2 * k;
+                if (ri < rcount) {
+                    const int mp = (r0 + ri) % maps;
+                    const float* qr = qs + ri * dim;
+                    float s = 0.f;
+                    for (int ch = 0; ch < dchunk; ++ch) {
+                        float kf[VEC];
+                        krow[mp * dchunk + ch].get(kf);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) s += qr[ch * VEC + e] * kf[e];
+                    }
+                    sc[ri * PG + my_key] = ok ? maps_cap(s, softcap, inv_cap) : -INFINITY;
+                }
+            }
+        }
+        __syncthreads();
+
+        for (int ri = warp; ri < rcount; ri += (blockDim.x >> 5)) {
+            float mx = -INFINITY;
+            for (int j = lane; j < n_keys; j += 32) mx = fmaxf(mx, sc[ri * PG + j]);
+            mx = warp_max(mx);
+            const float m_old = m_s[ri], m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+            for (int j = lane; j < n_keys; j += 32) {
+                const float sj = sc[ri * PG + j];
+                const float pj = (m_new == -INFINITY || sj == -INFINITY) ? 0.f : expf(sj - m_new);
+                sc[ri * PG + j] = pj;
+                sum += pj;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                const float alpha = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
+                a_s[ri] = alpha;
+                l_s[ri] = l_s[ri] * alpha + sum;
+                m_s[ri] = m_new;
+            }
+        }
+        __syncthreads();
+
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int d = tid + c * 128;
+            if (d < vdim) {
+#pragma unroll
+                for (int ri = 0; ri < RT; ++ri) if (ri < rcount) acc[ri][c] *= a_s[ri];
+                for (int j = 0; j < n_keys; ++j) {
+                    const float v = to_f32(Vt[(size_t)j * vdim + d]);
+#pragma unroll
+                    for (int ri = 0; ri < RT; ++ri) if (ri < rcount) acc[ri][c] += sc[ri * PG + j] * v;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    const size_t row_base = ((size_t)b * G + g) * rows_g + r0;        // rows of all heads: [B, H * maps]
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int d = tid + c * 128;
+        if (d >= vdim) continue;
+#pragma unroll
+        for (int ri = 0; ri < RT; ++ri)
+            if (ri < rcount) part_acc[((row_base + ri) * n_runs + run) * vdim + d] = acc[ri][c];
+    }
+    if (tid < rcount) {
+        const size_t at = (row_base + tid) * n_runs + run;
+        part_m[at] = m_s[tid];
+        part_l[at] = l_s[tid];
+    }
+}
+
+// Per (query head, sequence): each map's a = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M), M = max_r m_r, over the
+// sequence's runs in index order; then the difference of the maps, the norm and the factor.  grid (H, B), 128 threads.
+template <typename T>
+__global__ void maps_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m, const float* __restrict__ part_l,
+                                  const int* __restrict__ seq_len, T* __restrict__ out, int H, int maps, int vdim, int chunk, int n_runs,
+                                  float lambda, int norm_out, float eps, float out_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float red[32];
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int len = seq_len[b];
+    const int first = maps_first_key(len - 1, chunk);
+    const int rp = maps_run_pages(first, len);
+    const int runs = min(n_runs, ((len - 1) / QWB_MAPS_PAGE - first / QWB_MAPS_PAGE) / rp + 1);
+    float res[2] = {0.f, 0.f};
+    for (int mp = 0; mp < maps; ++mp) {
+        const size_t row = ((size_t)b * H + h) * maps + mp;
+        float M = -INFINITY;
+        for (int r = 0; r < runs; ++r) M = fmaxf(M, part_m[row * n_runs + r]);
+        float L = 0.f;
+        for (int r = 0; r < runs; ++r) L += part_l[row * n_runs + r] * expf(part_m[row * n_runs + r] - M);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int d = tid + c * 128;
+            if (d >= vdim) continue;
+            float a = 0.f;
+            for (int r = 0; r < runs; ++r) a += part_acc[(row * n_runs + r) * vdim + d] * expf(part_m[row * n_runs + r] - M);
+            a *= inv;
+            res[c] = mp == 0 ? a : res[c] - lambda * a;
+        }
+    }
+    float mul = 1.f;
+    if (norm_out) {
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) if (tid + c * 128 < vdim) ss += res[c] * res[c];
+        mul = rsqrtf(block_sum(ss, red) / (float)vdim + eps) * out_scale;
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int d = tid + c * 128;
+        if (d < vdim) out[((size_t)b * H + h) * vdim + d] = from_f32<T>(res[c] * mul);
+    }
+}
+
+// runs of the grid for sequences of up to max_len tokens
+extern "C" int qwb_maps_decode_runs(int max_len, int chunk) {
+    if (max_len <= 0) return 1;
+    // the most pages a sequence's visible keys touch: a chunk may begin anywhere in its first page
+    const int pages_all = (max_len + QWB_MAPS_PAGE - 1) / QWB_MAPS_PAGE;
+    const int pages = chunk > 0 ? min(pages_all, (chunk + QWB_MAPS_PAGE - 2) / QWB_MAPS_PAGE + 1) : pages_all;
+    const int runs = (pages + QWB_MAPS_RUN_PAGES - 1) / QWB_MAPS_RUN_PAGES;
+    return runs < QWB_MAPS_MAX_RUNS ? runs : QWB_MAPS_MAX_RUNS;
+}
+
+extern "C" long long qwb_maps_decode_scratch_floats(int B, int H, int maps, int vdim, int n_runs) {
+    return (long long)B * H * maps * n_runs * (vdim + 2);
+}
+
+template <typename T>
+static int launch_maps_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
+                              float* scratch, void* out, int B, int H, int G, int maps, int dim, int vdim, int table_width, float scale,
+                              float softcap, int chunk, int n_runs, float lambda, int norm_out, float eps, float out_scale,
+                              cudaStream_t stream) {
+    constexpr int VEC = Vec16<T>::N;
+    const int kdim = maps * dim;
+    const size_t rows = (size_t)B * H * maps;
+    float* part_acc = scratch;
+    float* part_m = part_acc + rows * n_runs * vdim;
+    float* part_l = part_m + rows * n_runs;
+    const size_t smem = ((size_t)QWB_MAPS_PAGE * (kdim + VEC) + (size_t)QWB_MAPS_PAGE * vdim) * sizeof(T) +
+                        ((size_t)QWB_MAPS_ROWS * dim + QWB_MAPS_ROWS * QWB_MAPS_PAGE + 3 * QWB_MAPS_ROWS) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(maps_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "maps_decode: %s", cudaGetErrorString(e));
+    }
+    const int rows_g = (H / G) * maps, slices = (rows_g + QWB_MAPS_ROWS - 1) / QWB_MAPS_ROWS;
+    qwb_launch(maps_decode_kernel<T>, dim3(n_runs, G * slices, B), 128, smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool,
+               page_table, seq_len, part_acc, part_m, part_l, H, G, maps, dim, vdim, table_width, scale, softcap, chunk, n_runs);
+    if (int rc = qwb_check_launch("maps_decode")) return rc;
+    qwb_launch(maps_merge_kernel<T>, dim3(H, B), 128, 0, stream, (const float*)part_acc, (const float*)part_m, (const float*)part_l,
+               seq_len, (T*)out, H, maps, vdim, chunk, n_runs, lambda, norm_out, eps, out_scale);
+    return qwb_check_launch("maps_merge");
+}
+
+// q [B, H, maps * dim]; out [B, H * vdim]; scratch: qwb_maps_decode_scratch_floats floats.
+extern "C" int qwb_maps_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
+                               float* scratch, void* out, int dtype, int B, int H, int G, int maps, int dim, int vdim, int table_width,
+                               float scale, float softcap, int chunk, int n_runs, float lambda, int norm_out, float eps, float out_scale,
+                               cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (int rc = check_maps_sizes("maps_decode", H, G, maps, dim, vdim, table_width, chunk)) return rc;
+    if (n_runs <= 0 || n_runs > 65535 || B > 65535) return qwb_fail(QWB_ERR_ARG, "maps_decode: %d runs, %d sequences", n_runs, B);
+    if (dtype == QWB_DT_F32)
+        return launch_maps_decode<float>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, H, G, maps, dim, vdim, table_width, scale,
+                                         softcap, chunk, n_runs, lambda, norm_out, eps, out_scale, stream);
+    if (dtype == QWB_DT_BF16)
+        return launch_maps_decode<bf16>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, H, G, maps, dim, vdim, table_width, scale,
+                                        softcap, chunk, n_runs, lambda, norm_out, eps, out_scale, stream);
+    return qwb_fail(QWB_ERR_ARG, "maps_decode: unknown dtype %d", dtype);
+}

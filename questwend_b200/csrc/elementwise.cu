@@ -3,13 +3,13 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------
-// h[t,:] = float(E[id_t,:]).  A row gather without scaling (the reference:
+// h[t,:] = float(E[id_t,:]) * scale.  A row gather (the reference, which does not scale:
 // core/runtime.cpp:1001, ggml-cuda/getrows.cu:73-102).  An id outside [0, V) writes a
 // row of zeros and records the first such token in *bad_token (if given).
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                    float* __restrict__ out, int D, int V, int* bad_token) {
+                                    float* __restrict__ out, int D, int V, int* bad_token, float scale) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -29,32 +29,70 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __rest
             src[i].get(v);
 #pragma unroll
             for (int e = 0; e < VEC; e += 4)
-                *reinterpret_cast<float4*>(o + (size_t)i * VEC + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                *reinterpret_cast<float4*>(o + (size_t)i * VEC + e) =
+                    make_float4(v[e] * scale, v[e + 1] * scale, v[e + 2] * scale, v[e + 3] * scale);
         }
         return;
     }
-    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
 extern "C" int qwb_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
-                                int T, int D, int V, int* bad_token, cudaStream_t stream) {
+                                int T, int D, int V, int* bad_token, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (D <= 0 || V <= 0) return qwb_fail(QWB_ERR_ARG, "embed_gather: bad sizes D=%d V=%d", D, V);
     const int block = D >= 1024 ? 256 : 128;
     if (table_dtype == QWB_DT_F32)
-        qwb_launch(embed_gather_kernel<float>, T, block, 0, stream, ids, (const float*)table, out, D, V, bad_token);
+        qwb_launch(embed_gather_kernel<float>, T, block, 0, stream, ids, (const float*)table, out, D, V, bad_token, scale);
     else if (table_dtype == QWB_DT_BF16)
-        qwb_launch(embed_gather_kernel<bf16>, T, block, 0, stream, ids, (const bf16*)table, out, D, V, bad_token);
+        qwb_launch(embed_gather_kernel<bf16>, T, block, 0, stream, ids, (const bf16*)table, out, D, V, bad_token, scale);
     else
         return qwb_fail(QWB_ERR_ARG, "embed_gather: unknown dtype %d", table_dtype);
     return qwb_check_launch("embed_gather");
 }
 
 // ---------------------------------------------------------------------------------
+// h[t,:] += float(E[id_t,:]) * scale + vec[:], in place on the 32-bit stream: what a pass of a looped run of layers adds
+// before its first layer (the tokens' embeddings once more and a vector of the pass).  table or vec may be null.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_add_kernel(const int* __restrict__ ids, const T* __restrict__ table, const float* __restrict__ vec,
+                                 float* h, int D, int V, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int id = table ? ids[t] : 0;
+    const bool row_ok = table && id >= 0 && id < V;
+    const T* row = table + (size_t)(row_ok ? id : 0) * D;
+    float* o = h + (size_t)t * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = o[i];
+        if (row_ok) v += to_f32(row[i]) * scale;
+        if (vec) v += vec[i];
+        o[i] = v;
+    }
+}
+
+extern "C" int qwb_embed_add(const int* ids, const void* table, int table_dtype, const float* vec, float* h, int T, int D, int V,
+                             float scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (D <= 0 || (table && (V <= 0 || !ids))) return qwb_fail(QWB_ERR_ARG, "embed_add: bad sizes D=%d V=%d", D, V);
+    if (!table && !vec) return 0;
+    const int block = D >= 1024 ? 256 : 128;
+    if (table_dtype == QWB_DT_F32)
+        qwb_launch(embed_add_kernel<float>, T, block, 0, stream, ids, (const float*)table, vec, h, D, V, scale);
+    else if (table_dtype == QWB_DT_BF16)
+        qwb_launch(embed_add_kernel<bf16>, T, block, 0, stream, ids, (const bf16*)table, vec, h, D, V, scale);
+    else
+        return qwb_fail(QWB_ERR_ARG, "embed_add: unknown dtype %d", table_dtype);
+    return qwb_check_launch("embed_add");
+}
+
+// ---------------------------------------------------------------------------------
 // RMS norm over rows of D:  y = v * rsqrt(mean(v^2) + eps) * w,  v = x (+ delta).
 // (the reference: core/runtime.cpp:1018-1019, ggml-cuda/norm.cu:76-155.)
 //   x      [rows_in, D] float   the residual stream
-//   delta  [rows_in, D] float   optional: the sum x + delta is formed in 32-bit first
+//   delta  [rows_in, D] float   optional: the sum x + delta_scale * delta is formed in 32-bit first
 //   planes [P, rows_in, D] float optional, instead of delta: a product that its kernel left as sums over pieces of k
 //                                (gemm_ring's split form); columns 16 t .. 16 t + 15 have plane_count[t] <= 4 planes, which
 //                                are added onto x in the order of the planes
@@ -87,7 +125,7 @@ template <typename TOut, bool VEC>
 __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* planes,
                                const unsigned char* __restrict__ plane_count, size_t plane_stride,
                                float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
-                               const int* __restrict__ rows, int D, float eps) {
+                               const int* __restrict__ rows, int D, float eps, float delta_scale) {
     pdl_launch_dependents();            // the trigger first: the kernel after this one may start before the one before it ends
     // the norm's weight is nobody's output: a thread's first pieces of it are on their way before the wait
     float4 w_first[RMS_W_FIRST];
@@ -114,7 +152,7 @@ __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* 
             // of 8 rows of 4,096 took 1.4 us longer under the ring fill of the product that follows (and with a thread's four
             // loads issued together, before the first store, a step took 0.5 % longer)
             float4 v = x4[i];
-            if (d4) { const float4 d = d4[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            if (d4) { const float4 d = d4[i]; v.x += delta_scale * d.x; v.y += delta_scale * d.y; v.z += delta_scale * d.z; v.w += delta_scale * d.w; }
             if (planes) {
                 const int n_planes = plane_count[4 * i / RMS_PLANE_COLS];
                 const float4* p4 = reinterpret_cast<const float4*>(planes + src) + i;
@@ -133,7 +171,7 @@ __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* 
     } else {
         for (int i = threadIdx.x; i < D; i += blockDim.x) {
             float v = x[src + i];
-            if (delta) v += delta[src + i];
+            if (delta) v += delta_scale * delta[src + i];
             if (planes)
                 for (int p = 0, n_planes = plane_count[i / RMS_PLANE_COLS]; p < n_planes; ++p) v += planes[p * plane_stride + src + i];
             if (sum_out) sum_out[src + i] = v;
@@ -171,7 +209,7 @@ template <typename TOut, int ITERS>
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_kernel(const float* x, const float* delta, const float* planes, const unsigned char* __restrict__ plane_count,
                     size_t plane_stride, float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
-                    const int* __restrict__ rows, int D, float eps) {
+                    const int* __restrict__ rows, int D, float eps, float delta_scale) {
     pdl_launch_dependents();            // the trigger first, and the weight asked for before the wait: as in rmsnorm_kernel
     float4 g[ITERS];
 #pragma unroll
@@ -195,7 +233,7 @@ rmsnorm_rows_kernel(const float* x, const float* delta, const float* planes, con
 #pragma unroll
         for (int k = 0; k < ITERS; ++k) {
             const int i = threadIdx.x + k * 256;
-            if (i < D / 4) { const float4 d = d4[i]; v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w; }
+            if (i < D / 4) { const float4 d = d4[i]; v[k].x += delta_scale * d.x; v[k].y += delta_scale * d.y; v[k].z += delta_scale * d.z; v[k].w += delta_scale * d.w; }
         }
     }
     if (planes) {                       // a product left as sums over pieces of k: a column's planes, in their order
@@ -235,7 +273,7 @@ rmsnorm_rows_kernel(const float* x, const float* delta, const float* planes, con
 template <typename TOut>
 static int launch_rmsnorm(const float* x, const float* delta, const float* planes, const unsigned char* plane_count,
                           size_t plane_stride, float* sum_out, const float* w, TOut* out, const int* rows,
-                          int n_rows, int D, float eps, size_t smem, cudaStream_t stream) {
+                          int n_rows, int D, float eps, float delta_scale, size_t smem, cudaStream_t stream) {
     const bool vec = D % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                      (!delta || (uintptr_t)delta % 16 == 0) && (!sum_out || (uintptr_t)sum_out % 16 == 0) &&
                      (!planes || ((uintptr_t)planes % 16 == 0 && plane_stride % 4 == 0));
@@ -243,39 +281,39 @@ static int launch_rmsnorm(const float* x, const float* delta, const float* plane
     const int block = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     cudaError_t e = cudaSuccess;
     if (vec && D / 4 <= 4 * 256) {
-        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_rows_kernel<TOut, 4>, n_rows, 256, 0, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
+        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_rows_kernel<TOut, 4>, n_rows, 256, 0, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps, delta_scale);
     } else if (vec && D / 4 <= 8 * 256) {
-        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_rows_kernel<TOut, 8>, n_rows, 256, 0, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
+        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_rows_kernel<TOut, 8>, n_rows, 256, 0, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps, delta_scale);
     } else if (vec) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_kernel<TOut, true>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
+        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_kernel<TOut, true>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps, delta_scale);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        qwb_launch(rmsnorm_kernel<TOut, false>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
+        qwb_launch(rmsnorm_kernel<TOut, false>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps, delta_scale);
     }
     return qwb_check_launch("rmsnorm");
 }
 
 static int rmsnorm_any(const float* x, const float* delta, const float* planes, const unsigned char* plane_count,
                        size_t plane_stride, float* sum_out, const float* w, void* out, int out_dtype, const int* rows,
-                       int n_rows, int D, float eps, cudaStream_t stream) {
+                       int n_rows, int D, float eps, float delta_scale, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm: bad width %d", D);
     const size_t smem = (size_t)D * sizeof(float);
     if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm: width %d does not fit in shared memory (max %d)", D, 200 * 1024 / 4);
     if (out_dtype == QWB_DT_F32)
-        return launch_rmsnorm<float>(x, delta, planes, plane_count, plane_stride, sum_out, w, (float*)out, rows, n_rows, D, eps, smem, stream);
+        return launch_rmsnorm<float>(x, delta, planes, plane_count, plane_stride, sum_out, w, (float*)out, rows, n_rows, D, eps, delta_scale, smem, stream);
     if (out_dtype == QWB_DT_BF16)
-        return launch_rmsnorm<bf16>(x, delta, planes, plane_count, plane_stride, sum_out, w, (bf16*)out, rows, n_rows, D, eps, smem, stream);
+        return launch_rmsnorm<bf16>(x, delta, planes, plane_count, plane_stride, sum_out, w, (bf16*)out, rows, n_rows, D, eps, delta_scale, smem, stream);
     return qwb_fail(QWB_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
 }
 
 extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, const float* w,
-                           void* out, int out_dtype, const int* rows, int n_rows, int D, float eps,
+                           void* out, int out_dtype, const int* rows, int n_rows, int D, float eps, float delta_scale,
                            cudaStream_t stream) {
-    return rmsnorm_any(x, delta, nullptr, nullptr, 0, sum_out, w, out, out_dtype, rows, n_rows, D, eps, stream);
+    return rmsnorm_any(x, delta, nullptr, nullptr, 0, sum_out, w, out, out_dtype, rows, n_rows, D, eps, delta_scale, stream);
 }
 
 // The same with a product in planes instead of delta: planes [n_planes, rows_in, D], plane_count [ceil(D / 16)] bytes.
@@ -284,7 +322,7 @@ extern "C" int qwb_rmsnorm_planes(const float* x, const float* planes, const uns
                                   int n_rows, int D, float eps, cudaStream_t stream) {
     if (n_planes < 1 || n_planes > RMS_MAX_PLANES)
         return qwb_fail(QWB_ERR_ARG, "rmsnorm: %d planes; this kernel adds up to %d", n_planes, RMS_MAX_PLANES);
-    return rmsnorm_any(x, nullptr, planes, plane_count, (size_t)rows_in * D, sum_out, w, out, out_dtype, rows, n_rows, D, eps, stream);
+    return rmsnorm_any(x, nullptr, planes, plane_count, (size_t)rows_in * D, sum_out, w, out, out_dtype, rows, n_rows, D, eps, 1.f, stream);
 }
 
 // x[t, :] += the planes of a product (as above), for a consumer that is not this norm.
@@ -313,8 +351,13 @@ extern "C" int qwb_add_planes(float* x, const float* planes, const unsigned char
 // interleave 0: the first F columns are the gate and the last F the up projection;
 // interleave G > 0 (F a multiple of G): for every G features, their G gates and then their G ups.
 // ---------------------------------------------------------------------------------
+// act 0: silu; 1: gelu (tanh form)
+__device__ __forceinline__ float gate_act(float g, int act) {
+    return act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.f + expf(-g));
+}
+
 template <typename TOut>
-__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int interleave) {
+__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int interleave, int act) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t n = (size_t)T * F;
@@ -323,7 +366,7 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__
         const size_t gate_at = interleave > 0 ? (f / interleave) * 2 * interleave + f % interleave : f;
         const float g = gu[t * 2 * F + gate_at];
         const float u = gu[t * 2 * F + gate_at + (interleave > 0 ? interleave : F)];
-        out[i] = from_f32<TOut>(g / (1.f + expf(-g)) * u);
+        out[i] = from_f32<TOut>(gate_act(g, act) * u);
     }
 }
 
@@ -331,7 +374,7 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__
 // takes 8 features: 64 bytes of gates and ups in four 16-byte loads, one store of 8 values.  64 rows of 12,288 features:
 // 3.2 us against 5.5 with a value a thread.
 template <typename TOut>
-__global__ void silu_mul_eights_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F) {
+__global__ void silu_mul_eights_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int act) {
     pdl_wait();
     pdl_launch_dependents();
     const int groups = F >> 3;
@@ -341,15 +384,14 @@ __global__ void silu_mul_eights_kernel(const float* __restrict__ gu, TOut* __res
         const float4* src = reinterpret_cast<const float4*>(gu + (t * 2 * F + grp * 16));
         const float4 g0 = src[0], g1 = src[1], u0 = src[2], u1 = src[3];
         TOut* dst = out + t * F + grp * 8;
-        Pack4<TOut>::store(dst, g0.x / (1.f + expf(-g0.x)) * u0.x, g0.y / (1.f + expf(-g0.y)) * u0.y,
-                           g0.z / (1.f + expf(-g0.z)) * u0.z, g0.w / (1.f + expf(-g0.w)) * u0.w);
-        Pack4<TOut>::store(dst + 4, g1.x / (1.f + expf(-g1.x)) * u1.x, g1.y / (1.f + expf(-g1.y)) * u1.y,
-                           g1.z / (1.f + expf(-g1.z)) * u1.z, g1.w / (1.f + expf(-g1.w)) * u1.w);
+        Pack4<TOut>::store(dst, gate_act(g0.x, act) * u0.x, gate_act(g0.y, act) * u0.y, gate_act(g0.z, act) * u0.z, gate_act(g0.w, act) * u0.w);
+        Pack4<TOut>::store(dst + 4, gate_act(g1.x, act) * u1.x, gate_act(g1.y, act) * u1.y, gate_act(g1.z, act) * u1.z, gate_act(g1.w, act) * u1.w);
     }
 }
 
-extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, int interleave, cudaStream_t stream) {
+extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, int interleave, int act, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (act != 0 && act != 1) return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown gate activation %d", act);
     if (F <= 0) return qwb_fail(QWB_ERR_ARG, "silu_mul: bad width %d", F);
     if (interleave < 0 || (interleave > 0 && F % interleave))
         return qwb_fail(QWB_ERR_ARG, "silu_mul: %d features cannot be interleaved in groups of %d", F, interleave);
@@ -359,34 +401,34 @@ extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int 
         (out_dtype == QWB_DT_F32 || out_dtype == QWB_DT_BF16)) {
         const size_t groups = n / 8;
         const int g8 = (int)((groups + block - 1) / block < 148 * 16 ? (groups + block - 1) / block : 148 * 16);
-        if (out_dtype == QWB_DT_F32) qwb_launch(silu_mul_eights_kernel<float>, g8, block, 0, stream, gate_up, (float*)out, T, F);
-        else qwb_launch(silu_mul_eights_kernel<bf16>, g8, block, 0, stream, gate_up, (bf16*)out, T, F);
+        if (out_dtype == QWB_DT_F32) qwb_launch(silu_mul_eights_kernel<float>, g8, block, 0, stream, gate_up, (float*)out, T, F, act);
+        else qwb_launch(silu_mul_eights_kernel<bf16>, g8, block, 0, stream, gate_up, (bf16*)out, T, F, act);
         return qwb_check_launch("silu_mul");
     }
     const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
     if (out_dtype == QWB_DT_F32)
-        qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F, interleave);
+        qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F, interleave, act);
     else if (out_dtype == QWB_DT_BF16)
-        qwb_launch(silu_mul_kernel<bf16>, grid, block, 0, stream, gate_up, (bf16*)out, T, F, interleave);
+        qwb_launch(silu_mul_kernel<bf16>, grid, block, 0, stream, gate_up, (bf16*)out, T, F, interleave, act);
     else
         return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown dtype %d", out_dtype);
     return qwb_check_launch("silu_mul");
 }
 
-// out[i] += delta[i]: the residual sum on its own, for blocks that end without a norm.
-__global__ void add_inplace_kernel(float* __restrict__ out, const float* __restrict__ delta, size_t n) {
+// out[i] += scale * delta[i]: the residual sum on its own, for blocks that end without a norm.
+__global__ void add_inplace_kernel(float* __restrict__ out, const float* __restrict__ delta, size_t n, float scale) {
     pdl_wait();
     pdl_launch_dependents();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        out[i] += delta[i];
+        out[i] += scale * delta[i];
 }
 
-extern "C" int qwb_add_inplace(float* out, const float* delta, long long n, cudaStream_t stream) {
+extern "C" int qwb_add_inplace(float* out, const float* delta, long long n, float scale, cudaStream_t stream) {
     if (n <= 0) return 0;
     const int block = 256;
     const long long want = (n + block - 1) / block;
     const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
-    qwb_launch(add_inplace_kernel, grid, block, 0, stream, out, delta, (size_t)n);
+    qwb_launch(add_inplace_kernel, grid, block, 0, stream, out, delta, (size_t)n, scale);
     return qwb_check_launch("add_inplace");
 }
 

@@ -348,10 +348,45 @@ extern "C" int qwb_delta_prep(float* qkv, int ld, float* kq, const float* b_raw,
     return qwb_check_launch("delta_prep");
 }
 
+// Preparation for gated linear attention, one block per token: q times q_scale in place, kq = k . q per head, and the
+// decay per head and key channel, decay = sigmoid(a_raw + a_bias)^(1 / tau), formed as exp(log_sigmoid(z) / tau) with
+// log_sigmoid(z) = -softplus(-z).  qkv [T, ld]: q [H * K] | k [H * K] | v.
+__global__ void gla_prep_kernel(float* qkv, int ld, float* __restrict__ kq, const float* __restrict__ a_raw, const float* __restrict__ a_bias,
+                                float* __restrict__ decay, int H, int K, float q_scale, float inv_tau) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    float* row = qkv + (size_t)t * ld;
+    for (int h = warp; h < H; h += nwarp) {
+        float* q = row + h * K;
+        const float* k = row + (H + h) * K;
+        float dot = 0.f;
+        for (int i = lane; i < K; i += 32) {
+            const float qs = q[i] * q_scale;
+            q[i] = qs;
+            dot += qs * k[i];
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) kq[(size_t)t * H + h] = dot;
+    }
+    for (int i = threadIdx.x; i < H * K; i += blockDim.x)
+        decay[(size_t)t * H * K + i] = expf(-softplus_f(-(a_raw[(size_t)t * H * K + i] + (a_bias ? a_bias[i] : 0.f))) * inv_tau);
+}
+
+extern "C" int qwb_gla_prep(float* qkv, int ld, float* kq, const float* a_raw, const float* a_bias, float* decay, int T, int H, int K,
+                            float q_scale, float tau, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || K <= 0 || !(tau > 0.f)) return qwb_fail(QWB_ERR_ARG, "gla_prep: %d heads of %d, tau %g", H, K, (double)tau);
+    qwb_launch(gla_prep_kernel, T, 128, 0, stream, qkv, ld, kq, a_raw, a_bias, decay, H, K, q_scale, 1.f / tau);
+    return qwb_check_launch("gla_prep");
+}
+
 // The recurrence, per head h (key head kh = h / (H / Hk)), per token, S is K x P:
 //     S = decay[:, None] * S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q
 // o is formed as (decayed S)^T q + u (k . q), so that both sums over the rows are taken in one pass.  A warp per
-// column, as above; state [slots, H, P, K].
+// column, as above; state [slots, H, P, K].  Without `beta` (null) the write is the plain outer product, u = v: gated
+// linear attention, S = decay[:, None] * S + k v^T.
 template <int PER, bool VEC, int TB, int CW>
 __global__ void __launch_bounds__(32 * QWB_SCAN_WARPS)
 delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ kq, const float* __restrict__ beta,
@@ -384,7 +419,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
             load_rows<PER, VEC>(decay + ((size_t)t * H + h) * K, n0, K, gn[j]);
 #pragma unroll
             for (int c = 0; c < CW; ++c) v_n[j][c] = row[v_at + c];
-            bt_n[j] = beta[(size_t)t * H + h]; kq_n[j] = kq[(size_t)t * Hk + kh];
+            bt_n[j] = beta ? beta[(size_t)t * H + h] : 0.f; kq_n[j] = kq[(size_t)t * Hk + kh];
         }
     };
     if (t0 < t1) load_round(t0);
@@ -428,7 +463,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
                 for (int c = 0; c < CW; ++c) { sk[c] = warp_sum(sk[c]); sq[c] = warp_sum(sq[c]); }
 #pragma unroll
                 for (int c = 0; c < CW; ++c) {
-                    const float u = bt[j] * (v[j][c] - sk[c]);
+                    const float u = beta ? bt[j] * (v[j][c] - sk[c]) : v[j][c];
 #pragma unroll
                     for (int k = 0; k < PER; ++k) s[c][k] += kk[j][k] * u;
                     if (lane == 0) o[((size_t)(tc + j) * H + h) * P + p0 + c] = sq[c] + u * kqv[j];
@@ -472,6 +507,7 @@ extern "C" int qwb_delta_scan(const float* qkv, int ld, const float* kq, const f
 // Gated norm over equal parts of a row.  y [T, n_parts * part] float, gate: column slice of a [T, ld_gate] matrix.
 //   mode 0: v = y * silu(gate); out = v / rms(v over the part) * w      (the gate before the norm)
 //   mode 1: out = y / rms(y over the part) * w * sigmoid(gate)          (the gate after the norm)
+//   mode 2: out = y / rms(y over the part) * w * silu(gate)
 // w has w_len entries and is indexed by column % w_len (the whole row, or one part shared by all parts).
 // One warp per (token, part).
 // ---------------------------------------------------------------------------------
@@ -497,7 +533,7 @@ __global__ void gated_part_norm_kernel(const float* __restrict__ y, const float*
     TOut* orow = out + (size_t)t * D + g * part;
     for (int i = lane; i < part; i += 32) {
         const float wi = w[(g * part + i) % w_len];
-        const float v = mode == 0 ? yr[i] * silu_f(gr[i]) * scale * wi : yr[i] * scale * wi * sigmoid_f(gr[i]);
+        const float v = mode == 0 ? yr[i] * silu_f(gr[i]) * scale * wi : yr[i] * scale * wi * (mode == 1 ? sigmoid_f(gr[i]) : silu_f(gr[i]));
         orow[i] = from_f32<TOut>(v);
     }
 }
@@ -505,7 +541,7 @@ __global__ void gated_part_norm_kernel(const float* __restrict__ y, const float*
 extern "C" int qwb_gated_part_norm(const float* y, const float* gate, int ld_gate, const float* w, int w_len, void* out,
                                    int out_dtype, int T, int n_parts, int part, float eps, int mode, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (n_parts <= 0 || part <= 0 || w_len <= 0 || (mode != 0 && mode != 1))
+    if (n_parts <= 0 || part <= 0 || w_len <= 0 || mode < 0 || mode > 2)
         return qwb_fail(QWB_ERR_ARG, "gated_part_norm: %d parts of %d, weight of %d, mode %d", n_parts, part, w_len, mode);
     const long long units = (long long)T * n_parts;
     const unsigned blocks = (unsigned)((units + 3) / 4);

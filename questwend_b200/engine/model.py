@@ -33,6 +33,7 @@ class Model:
         self.final_norm = build_part("norm", plan.final_norm, runtime)
         self.head = build_part("head", plan.head, runtime)
         self.schedule = list(plan.schedule)
+        self.before = [None if run.before is None else build_part("stream_step", run.before, runtime) for run in self.schedule]
 
     def _position(self, spec):
         key = (spec.kind, tuple(sorted(spec.params.items())))
@@ -42,7 +43,7 @@ class Model:
 
     # ---- weights
     def parts(self):
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        return [self.embedding, *self.blocks, *(b for b in self.before if b is not None), self.final_norm, self.head]
 
     def tensors(self) -> list[TensorSpec]:
         seen, out = set(), []
@@ -90,6 +91,8 @@ class Model:
         h = self.embedding.forward(ctx.token_ids)
         delta = None
         for i, run in enumerate(self.schedule):
+            if self.before[i] is not None:              # adds onto the stream; what is pending in ``delta`` stays pending
+                self.before[i].forward(h, ctx)
             h, delta = self.blocks[run.layer].forward(h, delta, ctx, unit_caches[i])
             if tap is not None:
                 if delta is not None:

@@ -5,8 +5,9 @@ An architecture's plan function turns its configuration into a ``ModelPlan``.
 one model can mix different mixers and feed-forwards.  ``schedule`` is the order
 of execution: a list of ``Run`` entries.  An entry may name a layer that another
 entry names too (the layer's weights are used twice; each run has a cache of its
-own), and it may set ``cache_of`` to an earlier entry to read that run's cache
-instead of owning one.
+own), it may set ``cache_of`` to an earlier entry to read that run's cache
+instead of owning one, and it may name a step that changes the residual stream
+right before it (``before``).
 """
 from __future__ import annotations
 
@@ -28,6 +29,8 @@ class LayerSpec:
 class Run:
     layer: int                           # index into ModelPlan.layers
     cache_of: int | None = None          # index into ModelPlan.schedule whose cache this run reads
+    before: PartSpec | None = None       # a step on the residual stream right before this run (family "stream_step"):
+                                         # what a looped run of layers adds when a pass opens
 
 
 @dataclass

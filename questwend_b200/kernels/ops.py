@@ -82,21 +82,43 @@ _f = ctypes.c_float
 
 
 # ----------------------------------------------------------------------------- elementwise
-def embed_gather(ids: torch.Tensor, table: torch.Tensor, bad_token: torch.Tensor | None = None) -> torch.Tensor:
-    """Rows of ``table`` [V, D] for int32 ``ids`` [T], as float32 [T, D]."""
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, bad_token: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """Rows of ``table`` [V, D] for int32 ``ids`` [T], times ``scale``, as float32 [T, D]."""
     _need(ids, "ids", torch.int32, 1)
     _need(table, "table", ndim=2)
     T, (V, D) = ids.numel(), table.shape
     out = torch.empty((T, D), dtype=torch.float32, device=table.device)
     _call("elementwise", "qwb_embed_gather", _ptr(ids), _ptr(table), _i(_dt(table.dtype)), _ptr(out),
-          _i(T), _i(D), _i(V), _ptr(bad_token), _stream())
+          _i(T), _i(D), _i(V), _ptr(bad_token), _f(scale), _stream())
     return out
+
+
+def embed_add(h: torch.Tensor, ids: torch.Tensor | None, table: torch.Tensor | None, scale: float = 1.0,
+              vec: torch.Tensor | None = None) -> torch.Tensor:
+    """In place on the float32 stream ``h`` [T, D]: h[t] += table[ids[t]] * scale + vec.  ``table`` (with ``ids``) or
+    ``vec`` (float32 [D]) may be None."""
+    _need(h, "h", torch.float32, 2)
+    T, D = h.shape
+    V = 0
+    if table is not None:
+        _need(ids, "ids", torch.int32, 1)
+        _need(table, "table", ndim=2)
+        V = table.shape[0]
+        if table.shape[1] != D or ids.numel() != T:
+            raise KernelError(f"embed_add: table {tuple(table.shape)}, {ids.numel()} ids for a stream {tuple(h.shape)}")
+    if vec is not None:
+        _need(vec, "vec", torch.float32, 1)
+        if vec.numel() != D:
+            raise KernelError(f"embed_add: a vector of {vec.numel()} for rows of {D}")
+    _call("elementwise", "qwb_embed_add", _ptr(ids if table is not None else None), _ptr(table),
+          _i(_dt(table.dtype) if table is not None else DT_F32), _ptr(vec), _ptr(h), _i(T), _i(D), _i(V), _f(scale), _stream())
+    return h
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
             delta: torch.Tensor | None = None, write_sum: bool = False,
-            rows: torch.Tensor | None = None) -> torch.Tensor:
-    """RMS norm of the rows of float32 ``x`` [T, D] (plus ``delta``), times ``weight``.
+            rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> torch.Tensor:
+    """RMS norm of the rows of float32 ``x`` [T, D] (plus ``delta_scale`` times ``delta``), times ``weight``.
 
     With ``write_sum`` the sum x + delta replaces x.  With ``rows`` (int32) only
     those rows are normed and the output has one row per entry.  ``delta`` may be a ``SplitSum``
@@ -124,7 +146,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
         if delta.shape != x.shape:
             raise KernelError(f"rmsnorm: delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
     _call("elementwise", "qwb_rmsnorm", _ptr(x), _ptr(delta), _ptr(x if (write_sum and delta is not None) else None),
-          _ptr(weight), _ptr(out), _i(_dt(out_dtype)), _ptr(rows), _i(n_rows), _i(D), _f(eps), _stream())
+          _ptr(weight), _ptr(out), _i(_dt(out_dtype)), _ptr(rows), _i(n_rows), _i(D), _f(eps), _f(delta_scale), _stream())
     return out
 
 
@@ -140,25 +162,31 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GATE_U
     return torch.cat([gate.reshape(F // group, group, K), up.reshape(F // group, group, K)], dim=1).reshape(2 * F, K).contiguous()
 
 
-def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0) -> torch.Tensor:
-    """silu(gate) * up from a float32 [T, 2F] matrix: gate columns first (``interleave`` 0), or for every
-    ``interleave`` features their gates and then their ups."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}      # what a gated feed-forward may put on its gate
+
+
+def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0, activation: str = "silu") -> torch.Tensor:
+    """act(gate) * up from a float32 [T, 2F] matrix: gate columns first (``interleave`` 0), or for every
+    ``interleave`` features their gates and then their ups.  ``activation``: one of ``GATE_ACTIVATIONS``."""
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"silu_mul: unknown gate activation '{activation}'")
     _need(gate_up, "gate_up", torch.float32, 2)
     T, F2 = gate_up.shape
     if F2 % 2:
         raise KernelError(f"silu_mul: {F2} columns cannot be split into gate and up")
     out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
     _call("elementwise", "qwb_silu_mul", _ptr(gate_up), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(F2 // 2), _i(interleave),
-          _stream())
+          _i(GATE_ACTIVATIONS[activation]), _stream())
     return out
 
 
-def add_inplace(out: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+def add_inplace(out: torch.Tensor, delta: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out += scale * delta, float32, in place."""
     _need(out, "out", torch.float32)
     _need(delta, "delta", torch.float32)
     if out.shape != delta.shape:
         raise KernelError(f"add_inplace: shapes {tuple(out.shape)} and {tuple(delta.shape)} differ")
-    _call("elementwise", "qwb_add_inplace", _ptr(out), _ptr(delta), ctypes.c_longlong(out.numel()), _stream())
+    _call("elementwise", "qwb_add_inplace", _ptr(out), _ptr(delta), ctypes.c_longlong(out.numel()), _f(scale), _stream())
     return out
 
 
@@ -843,11 +871,46 @@ def delta_rule(qkv: torch.Tensor, b_raw: torch.Tensor, b_col0: int, a_raw: torch
     return o
 
 
+def gla_scan(qkv: torch.Tensor, a_raw: torch.Tensor, a_bias: torch.Tensor | None, state: torch.Tensor, ctx, heads: int,
+             key_dim: int, vdim: int, q_scale: float, tau: float, write_state: bool = True) -> torch.Tensor:
+    """Gated linear attention over a step's tokens: per head S = diag(decay) S + k v^T, o = S^T (q * q_scale), with one
+    decay per head and key channel, decay = sigmoid(a_raw + a_bias)^(1 / tau).  ``qkv`` float32 [T, ld] whose first
+    2 * heads * key_dim + heads * vdim columns are q | k | v (q is scaled in place; further columns are left alone);
+    ``a_raw`` float32 [T, heads * key_dim]; ``state`` float32 [slots, heads, vdim, key_dim] (column by column) is read and
+    written back.  Returns o float32 [T, heads * vdim].  The recurrence is the delta rule's kernel without its correction
+    term."""
+    _need(qkv, "qkv", torch.float32, 2)
+    _need(a_raw, "a_raw", torch.float32, 2)
+    _need(state, "state", torch.float32, 4)
+    T = qkv.shape[0]
+    if (qkv.shape[1] < heads * (2 * key_dim + vdim) or tuple(a_raw.shape) != (T, heads * key_dim)
+            or tuple(state.shape[1:]) != (heads, vdim, key_dim)):
+        raise KernelError(f"gla_scan: qkv {tuple(qkv.shape)}, a {tuple(a_raw.shape)}, state {tuple(state.shape)} do not fit "
+                          f"{heads} heads of {key_dim} x {vdim}")
+    if a_bias is not None:
+        _need(a_bias, "a_bias", torch.float32, 1)
+        if a_bias.numel() != heads * key_dim:
+            raise KernelError(f"gla_scan: a bias of {a_bias.numel()} for {heads} heads of {key_dim}")
+    dev = qkv.device
+    kq = torch.empty((T, heads), dtype=torch.float32, device=dev)
+    decay = torch.empty((T, heads * key_dim), dtype=torch.float32, device=dev)
+    _call("recurrent", "qwb_gla_prep", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(a_raw), _ptr(a_bias), _ptr(decay), _i(T),
+          _i(heads), _i(key_dim), _f(q_scale), _f(tau), _stream())
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=dev)
+    _call("recurrent", "qwb_delta_scan", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(None), _ptr(decay), _ptr(state),
+          _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(o), _i(ctx.n_seqs), _i(heads), _i(heads), _i(key_dim), _i(vdim),
+          _i(1 if write_state else 0), _stream())
+    return o
+
+
 def gated_part_norm(y: torch.Tensor, gate: torch.Tensor, gate_col0: int, weight: torch.Tensor, n_parts: int, eps: float,
-                    gate_first: bool, out_dtype: torch.dtype) -> torch.Tensor:
+                    gate_first: bool, out_dtype: torch.dtype, gate_activation: str = "sigmoid") -> torch.Tensor:
     """RMS norm over ``n_parts`` equal parts of every row of float32 ``y`` [T, D], with a gate from columns
     ``gate_col0 ..`` of float32 ``gate`` [T, ld].  ``gate_first``: y * silu(gate) is normed, times the weight; else y is
-    normed, times the weight, times sigmoid(gate).  ``weight`` has D entries, or D / n_parts shared by all parts."""
+    normed, times the weight, times sigmoid(gate) (or silu(gate): ``gate_activation`` "silu").  ``weight`` has D entries,
+    or D / n_parts shared by all parts."""
+    if gate_activation not in ("sigmoid", "silu"):
+        raise KernelError(f"gated_part_norm: unknown gate activation '{gate_activation}'")
     _need(y, "y", torch.float32, 2)
     _need(gate, "gate", torch.float32, 2)
     _need(weight, "weight", torch.float32, 1)
@@ -858,7 +921,7 @@ def gated_part_norm(y: torch.Tensor, gate: torch.Tensor, gate_col0: int, weight:
     out = torch.empty((T, D), dtype=out_dtype, device=y.device)
     _call("recurrent", "qwb_gated_part_norm", _ptr(y), ctypes.c_void_p(gate.data_ptr() + 4 * gate_col0), _i(gate.shape[1]),
           _ptr(weight), _i(weight.numel()), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(n_parts), _i(D // n_parts), _f(eps),
-          _i(0 if gate_first else 1), _stream())
+          _i(0 if gate_first else (2 if gate_activation == "silu" else 1)), _stream())
     return out
 
 
@@ -1007,6 +1070,90 @@ def pool_attention(q: torch.Tensor, k_pool, v_pool, pk_pool, pv_pool, page_table
           _ptr(block_table), _ptr(ctx.cu_seqlens), _ptr(ctx.pos0), _ptr(cos_v), _ptr(sin_v), _ptr(out), _i(_dt(q.dtype)),
           _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G), _i(dim), _i(vdim), _i(width), _f(scale), _i(window), _i(pool),
           _i(1 if interleaved else 0), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- attention with score maps
+MAPS_MAX_DIM = 256          # csrc/attention_maps.cu: QWB_MAPS_MAX_DIM
+MAPS_MAX = 2                # ... QWB_MAPS_MAX: score maps per head
+
+
+def maps_prep(qkv: torch.Tensor, bias, q_weight, k_weight, cos, sin, ctx, page_table, k_pool, v_pool, n_heads: int,
+              n_kv_heads: int, maps: int, dim: int, vdim: int, rotary_dim: int, interleaved: bool, eps: float,
+              store_kv: bool = True) -> torch.Tensor:
+    """Bias (float32 over all columns, or None), per-map RMS norm of q and k (weights [dim] shared by heads and maps, or
+    None), rotation of the first ``rotary_dim`` values of every map of q and k, cache write.  ``qkv`` float32
+    [T, (H + G) * maps * dim + G * vdim]; the pools [pages, G, 64, maps * dim] / [pages, G, 64, vdim].  Returns q
+    [T, H, maps * dim] in the cache's dtype."""
+    _need(qkv, "qkv", torch.float32, 2)
+    T = qkv.shape[0]
+    ld = (n_heads + n_kv_heads) * maps * dim + n_kv_heads * vdim
+    if qkv.shape[1] != ld:
+        raise KernelError(f"maps_prep: qkv {tuple(qkv.shape)} for {n_heads}+{n_kv_heads} heads of {maps} x {dim}, values of {vdim}")
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE_SIZE, maps * dim) or tuple(v_pool.shape[1:]) != (n_kv_heads, PAGE_SIZE, vdim):
+        raise KernelError(f"maps_prep: pools {tuple(k_pool.shape)}, {tuple(v_pool.shape)} do not fit")
+    for name, t, n in (("bias", bias, ld), ("q_weight", q_weight, dim), ("k_weight", k_weight, dim)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != n:
+                raise KernelError(f"maps_prep: {name} of {t.numel()}, wanted {n}")
+    if cos is None:
+        rotary_dim = 0
+    for name, t in (("cos", cos), ("sin", sin)):
+        if t is not None:
+            _need(t, name, torch.float32, 2)
+            if tuple(t.shape) != (T, rotary_dim // 2):
+                raise KernelError(f"maps_prep: table {name} {tuple(t.shape)} for {T} tokens and {rotary_dim} turned values")
+    q = torch.empty((T, n_heads, maps * dim), dtype=k_pool.dtype, device=qkv.device)
+    _call("attention_maps", "qwb_maps_prep", _ptr(qkv), _ptr(bias), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
+          _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(page_table), _i(page_table.shape[1]), _ptr(q), _ptr(k_pool), _ptr(v_pool),
+          _i(_dt(k_pool.dtype)), _i(T), _i(n_heads), _i(n_kv_heads), _i(maps), _i(dim), _i(vdim), _i(rotary_dim),
+          _i(1 if interleaved else 0), _f(eps), _i(1 if store_kv else 0), _stream())
+    return q
+
+
+def maps_prefill_mma_fits(dtype: torch.dtype, maps: int, dim: int, vdim: int) -> bool:
+    """Whether prompts take the tensor-core kernel: bfloat16, keys in multiples of 16, values of 8, tiles that fit."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(_lookup("attention_maps", "qwb_maps_prefill_mma_fits")[1](_i(DT_BF16), _i(maps), _i(dim), _i(vdim)))
+
+
+def maps_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, maps: int, scale: float, softcap: float = 0.0,
+                   chunk: int = 0, lam: float = 0.0, norm_out: bool = False, eps: float = 0.0, out_scale: float = 1.0,
+                   impl: str = "auto") -> torch.Tensor:
+    """Attention of a step's tokens with ``maps`` score maps per head over the same values.  ``q`` [T, H, maps * dim] in
+    the cache's dtype; returns [T, H * vdim] in that dtype: map 0's output, minus ``lam`` times map 1's if there are two,
+    then (``norm_out``) divided by its root mean square over vdim and multiplied by ``out_scale``.  Scores are scaled,
+    soft-capped (``softcap`` > 0) and masked causally, and to the query's chunk of ``chunk`` positions if that is > 0.
+    Steps of one token per sequence take the kernel that cuts the keys into runs; other steps the tensor-core kernel
+    where it fits (``impl`` "auto" or "mma"), else the plain one ("plain")."""
+    _need(q, "q", k_pool.dtype, 3)
+    T, H, kdim = q.shape
+    G, vdim = k_pool.shape[1], v_pool.shape[3]
+    if kdim % maps or k_pool.shape[3] != kdim:
+        raise KernelError(f"maps_attention: q {tuple(q.shape)} and keys {tuple(k_pool.shape)} with {maps} maps")
+    dim = kdim // maps
+    out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
+    width = page_table.shape[1]
+    if ctx.single_token:
+        lib = _lookup("attention_maps", "qwb_maps_decode_runs")[0]
+        n_runs = lib.qwb_maps_decode_runs(_i(ctx.max_len), _i(chunk))
+        lib.qwb_maps_decode_scratch_floats.restype = ctypes.c_longlong
+        scratch = torch.empty((lib.qwb_maps_decode_scratch_floats(_i(T), _i(H), _i(maps), _i(vdim), _i(n_runs)),),
+                              dtype=torch.float32, device=q.device)
+        _call("attention_maps", "qwb_maps_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.seq_len),
+              _ptr(scratch), _ptr(out), _i(_dt(q.dtype)), _i(T), _i(H), _i(G), _i(maps), _i(dim), _i(vdim), _i(width), _f(scale),
+              _f(softcap), _i(chunk), _i(n_runs), _f(lam), _i(1 if norm_out else 0), _f(eps), _f(out_scale), _stream(), kernels=2)
+        return out
+    if impl == "mma" or (impl == "auto" and maps_prefill_mma_fits(q.dtype, maps, dim, vdim)):
+        _call("attention_maps", "qwb_maps_prefill_mma", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
+              _ptr(ctx.pos0), _ptr(out), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G), _i(maps), _i(dim), _i(vdim), _i(width),
+              _f(scale), _f(softcap), _i(chunk), _f(lam), _i(1 if norm_out else 0), _f(eps), _f(out_scale), _stream())
+        return out
+    _call("attention_maps", "qwb_maps_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
+          _ptr(ctx.pos0), _ptr(out), _i(_dt(q.dtype)), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G), _i(maps), _i(dim), _i(vdim),
+          _i(width), _f(scale), _f(softcap), _i(chunk), _f(lam), _i(1 if norm_out else 0), _f(eps), _f(out_scale), _stream())
     return out
 
 

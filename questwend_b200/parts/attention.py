@@ -9,9 +9,9 @@ import math
 import torch
 
 from ..kernels import ops
-from ..kernels.limits import head_dim_refusal, pool_attention_refusal
+from ..kernels.limits import conv_taps_refusal, head_dim_refusal, maps_attention_refusal, pool_attention_refusal
 from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
-from .base import KVSpec, Mixer, take_weight
+from .base import KVSpec, Mixer, StateSpec, take_weight
 from .linear import kernel_modules as linear_modules, linear, linear_onto
 from .registry import register_mixer
 
@@ -216,5 +216,133 @@ class WindowPoolAttention(Mixer):
         return linear(att, self.w_o)
 
 
+class ScoreMapsAttention(Mixer):
+    """Grouped-query softmax attention whose heads carry ``maps`` score maps (1 or 2) over the same values.  A query head
+    has ``maps`` query vectors of ``head_dim`` values laid out one after the other, a key head as many key vectors; each
+    map is an attention of its own (score = q . k * ``scale``, then ``softcap`` * tanh(score / ``softcap``) if that is
+    > 0, a causal mask, and with ``chunk`` > 0 only the keys of the query's own block of ``chunk`` positions, counted
+    from the sequence's start).  With two maps the head's output is differential: a1 - lambda * a2 with
+    lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff`` (four learned vectors of the layer), divided by its root mean
+    square over the value size (eps inside the root) and multiplied by 1 - ``diff``.  In front of the scores, in this
+    order and each optional: biases on q, k and v, a short causal convolution over time on every channel of q, k and v
+    (``conv`` taps, no activation; its last inputs are per-sequence state), an RMS norm of every map of q and k with a
+    weight shared by heads and maps, and a rotation of the first part of every map.
+
+    params: hidden_size, n_heads, n_kv_heads, head_dim, value_dim, maps (default 1), biases (q, k, v), out_bias, conv
+    (0: none), qk_norm, norm_eps, scale (default 1/sqrt(head_dim)), softcap (0: none), chunk (0: plain causal), diff,
+    layout ("halves": pairs (i, i + n/2); "interleaved": (2i, 2i + 1)), names (optional overrides).  ``position``: an
+    encoding that gives cos and sin [T, n/2].
+    The cache: keys (all maps of a head in one row) and values per token; with a convolution also its tail."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "o_bias": "o.b",
+             "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "q_norm": "q.norm", "k_norm": "k.norm",
+             "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
+    LAYOUTS = ("halves", "interleaved")
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads, self.n_kv_heads = int(p["n_heads"]), int(p["n_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.value_dim = int(p.get("value_dim", self.head_dim))
+        self.maps = int(p.get("maps", 1))
+        self.biases, self.out_bias = bool(p.get("biases", False)), bool(p.get("out_bias", False))
+        self.taps = int(p.get("conv", 0) or 0)
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("norm_eps", 0.0))
+        self.scale = float(p.get("scale", 1.0 / math.sqrt(self.head_dim)))
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        self.chunk = int(p.get("chunk", 0) or 0)
+        self.diff = float(p.get("diff", 0.0))
+        self.layout = str(p.get("layout", "halves"))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        self.position = position[0] if isinstance(position, (tuple, list)) else position
+        self.rotary_dim = getattr(self.position, "rotary_dim", 0) if self.position is not None else 0
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} key/value heads")
+        if self.layout not in self.LAYOUTS:
+            raise ValueError(f"attention '{self.prefix}': layout '{self.layout}' is not one of {', '.join(self.LAYOUTS)}")
+        for refusal in (maps_attention_refusal(self.maps, self.head_dim, self.value_dim),
+                        conv_taps_refusal(self.taps) if self.taps else None):
+            if refusal:
+                raise ValueError(f"attention '{self.prefix}': {refusal}")
+        if self.rotary_dim > self.head_dim:
+            raise ValueError(f"rotary size {self.rotary_dim} exceeds the map size {self.head_dim}")
+        self.n_q = self.n_heads * self.maps * self.head_dim
+        self.n_k = self.n_kv_heads * self.maps * self.head_dim
+        self.n_v = self.n_kv_heads * self.value_dim
+        self.channels = self.n_q + self.n_k + self.n_v
+        self.lam = 0.0
+
+    def tensors(self):
+        n, px, D = self.names, self.prefix, self.hidden
+        sizes = {"q": self.n_q, "k": self.n_k, "v": self.n_v}
+        out = [TensorSpec(px + n[x], (sizes[x], D), MATRIX) for x in "qkv"]
+        out.append(TensorSpec(px + n["o"], (D, self.n_heads * self.value_dim), MATRIX))
+        if self.biases:
+            out += [TensorSpec(px + n[x + "_bias"], (sizes[x],), VECTOR) for x in "qkv"]
+        if self.out_bias:
+            out.append(TensorSpec(px + n["o_bias"], (D,), VECTOR))
+        if self.taps:
+            out += [TensorSpec(px + n[x + "_conv"], (sizes[x], self.taps), VECTOR) for x in "qkv"]
+        if self.qk_norm:
+            out += [TensorSpec(px + n["q_norm"], (self.head_dim,), VECTOR, NORM_WEIGHT),
+                    TensorSpec(px + n["k_norm"], (self.head_dim,), VECTOR, NORM_WEIGHT)]
+        if self.maps == 2:
+            out += [TensorSpec(px + n[x], (self.head_dim,), VECTOR) for x in ("lq1", "lk1", "lq2", "lk2")]
+        return out
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+
+        def f32(name):
+            return weights[px + n[name]].to(torch.float32).contiguous()
+
+        self.w_qkv = torch.cat([take_weight(weights, px + n[x]) for x in "qkv"], dim=0).contiguous()
+        self.w_o = weights[px + n["o"]]
+        self.b_qkv = torch.cat([f32(x + "_bias") for x in "qkv"]).contiguous() if self.biases else None
+        self.b_o = f32("o_bias") if self.out_bias else None
+        self.conv_w = torch.cat([f32(x + "_conv") for x in "qkv"], dim=0).contiguous() if self.taps else None
+        self.q_norm_w = f32("q_norm") if self.qk_norm else None
+        self.k_norm_w = f32("k_norm") if self.qk_norm else None
+        if self.maps == 2:      # one number for the layer, made once, in 64-bit on the host
+            lq1, lk1, lq2, lk2 = (weights[px + n[x]].to(torch.float64).cpu() for x in ("lq1", "lk1", "lq2", "lk2"))
+            self.lam = math.exp(float((lq1 * lk1).sum())) - math.exp(float((lq2 * lk2).sum())) + self.diff
+
+    def kernel_modules(self):
+        return ("attention_maps", "rope_kv", "elementwise", *(("recurrent",) if self.taps else ()),
+                *linear_modules(self.runtime.dtype))
+
+    def kv_spec(self):
+        return KVSpec(self.n_kv_heads, self.maps * self.head_dim, 0, value_dim=self.value_dim)
+
+    def state_spec(self):
+        return StateSpec((self.taps - 1, self.channels), torch.float32) if self.taps > 1 else None
+
+    def forward(self, x, ctx, cache):
+        qkv = linear(x, self.w_qkv)
+        bias = self.b_qkv
+        if self.taps:
+            tail = cache.state if self.taps > 1 else qkv.new_zeros((1, 0, self.channels))
+            qkv = ops.short_conv(qkv, 0, self.channels, self.conv_w, None, tail, ctx, activation=False,
+                                 update_tail=cache.writable, in_bias=bias)
+            bias = None
+        cos = sin = None
+        if self.position is not None and self.rotary_dim:
+            cos, sin = self.position.prepare(ctx)
+        table = ctx.page_tables[cache.group_id]
+        q = ops.maps_prep(qkv, bias, self.q_norm_w, self.k_norm_w, cos, sin, ctx, table, cache.k_pool, cache.v_pool,
+                          self.n_heads, self.n_kv_heads, self.maps, self.head_dim, self.value_dim, self.rotary_dim,
+                          self.layout == "interleaved", self.eps, store_kv=cache.writable)
+        two = self.maps == 2
+        att = ops.maps_attention(q, cache.k_pool, cache.v_pool, table, ctx, self.maps, self.scale, softcap=self.softcap,
+                                 chunk=self.chunk, lam=self.lam, norm_out=two, eps=self.eps,
+                                 out_scale=(1.0 - self.diff) if two else 1.0)
+        out = linear(att, self.w_o)
+        return ops.bias_act(out, self.b_o, "none", torch.float32) if self.b_o is not None else out
+
+
 register_mixer("gqa", GroupedQueryAttention)
 register_mixer("window_pool_attention", WindowPoolAttention)
+register_mixer("score_maps_attention", ScoreMapsAttention)

@@ -163,11 +163,26 @@ class NormedSum:
         return h
 
 
+class ScaledSum:
+    """A layer's output that is still to be multiplied by a constant and added onto the stream: h += scale * y.  A
+    block whose residual sum carries a factor hands this on as ``delta``; a norm that says ``adds_scaled_sums`` forms the
+    sum in its own pass over the row, anyone else calls ``add_onto``."""
+    __slots__ = ("y", "scale")
+
+    def __init__(self, y: torch.Tensor, scale: float):
+        self.y, self.scale = y, float(scale)
+
+    def add_onto(self, h: torch.Tensor) -> torch.Tensor:
+        from ..kernels import ops
+        return ops.add_inplace(h, self.y, self.scale)
+
+
 class Norm(Part):
     """y = norm(x + delta) over rows; x float32 [T, D]."""
 
     adds_split_sums = False     # True: ``delta`` may also be a SplitSum (a product left as sums over pieces of k)
     adds_normed_sums = False    # True: ``delta`` may also be a NormedSum whose norm is of this class
+    adds_scaled_sums = False    # True: ``delta`` may also be a ScaledSum
 
     def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None) -> torch.Tensor:
         raise NotImplementedError
@@ -210,6 +225,14 @@ class FeedForward(Part):
     adds_to_residual = False    # as for Mixer
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class StreamStep(Part):
+    """Something done to the residual stream between two scheduled runs (a run's ``before``): x float32 [T, D] is changed
+    in place.  What is still to be added onto the stream at that point stays pending; a step only adds."""
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> None:
         raise NotImplementedError
 
 

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from dataclasses import replace
 
-from .base import Block, NormedSum
+from .base import Block, NormedSum, ScaledSum
 from .linear import settle
 from .registry import build_part, register_block
 
@@ -153,6 +153,54 @@ class SandwichNormBlock(Block):
         return h, delta
 
 
+class ParallelResidualBlock(Block):
+    """x = norm(h); h += mult * (mixer(x) + feed_forward(x)): one norm, both sublayers read its output, and their sum,
+    times a constant, goes onto the stream.  The sum onto the stream is not made here: it is handed on as a
+    ``ScaledSum``, so that the next norm (of the next block, or the model's last) multiplies, adds and norms in one pass
+    over the row.  A feed-forward that can add its last product onto something adds it onto the mixer's output.  A layer
+    without a feed-forward (``feed_forward`` None) has the mixer only.
+    params: norm (the norm's tensor name after the layer's prefix), mixer_prefix, ffn_prefix, residual_mult (default 1)."""
+
+    def __init__(self, spec, runtime, layer=None, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        px = spec.prefix
+        self.mult = float(p.get("residual_mult", 1.0))
+        self.norm1 = build_part("norm", replace(layer.norm, prefix=px, params={**dict(layer.norm.params), "name": p.get("norm", "norm1")}),
+                                runtime)
+        self.mixer = build_part("mixer", replace(layer.mixer, prefix=px + p.get("mixer_prefix", "mix") + "."),
+                                runtime, position=position)
+        self.ffn = None
+        if layer.feed_forward is not None:
+            self.ffn = build_part("feed_forward", replace(layer.feed_forward, prefix=px + p.get("ffn_prefix", "mlp") + "."), runtime)
+
+    def parts(self):
+        return [part for part in (self.norm1, self.mixer, self.ffn) if part is not None]
+
+    def tensors(self):
+        return [t for part in self.parts() for t in part.tensors()]
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+
+    def kernel_modules(self):
+        return ("elementwise", *(m for part in self.parts() for m in part.kernel_modules()))
+
+    def forward(self, h, delta, ctx, cache):
+        x = self.norm1.forward(h, settle(h, delta, self.norm1), write_sum=True)
+        y = self.mixer.forward(x, ctx, cache)
+        if self.ffn is not None:
+            if self.ffn.adds_to_residual:
+                rest = self.ffn.forward(x, ctx, residual=y)     # None: added onto y in the last product's epilogue
+                if rest is not None:
+                    y = rest.add_onto(y) if hasattr(rest, "add_onto") else y.add_(rest)
+            else:
+                y = y.add_(self.ffn.forward(x, ctx))
+        return h, ScaledSum(y, self.mult)
+
+
 register_block("pre_norm", PreNormBlock)
 register_block("sandwich_norm", SandwichNormBlock)
 register_block("output_norm", OutputNormBlock)
+register_block("parallel_residual", ParallelResidualBlock)

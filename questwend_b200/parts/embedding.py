@@ -5,20 +5,21 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..weights.manifest import MATRIX, TensorSpec
-from .base import Part
+from ..weights.manifest import MATRIX, VECTOR, TensorSpec
+from .base import Part, StreamStep
 from .linear import kernel_modules as linear_modules, linear
-from .registry import register_embedding, register_head
+from .registry import register_embedding, register_head, register_stream_step
 
 
 class TokenEmbedding(Part):
-    """params: vocab_size, hidden_size, name."""
+    """params: vocab_size, hidden_size, name, scale (the rows are multiplied by it; default 1)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.name = self.prefix + spec.params.get("name", "embed_tokens.weight")
+        self.scale = float(spec.params.get("scale", 1.0))
         self.table = None
 
     def tensors(self):
@@ -31,7 +32,46 @@ class TokenEmbedding(Part):
         return ("elementwise",)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return ops.embed_gather(token_ids, self.table)
+        return ops.embed_gather(token_ids, self.table, scale=self.scale)
+
+
+class EmbeddingReinjection(StreamStep):
+    """Adds onto the stream, in place and 32-bit: the step's token embeddings again (``add_embedding``: the table's rows
+    times ``scale``, as the embedding made them) and row ``row`` of a learned table of vectors [rows, hidden_size]
+    (``vector``: its tensor name; None for no vector).  A looped run of layers opens each of its passes with this.
+    params: vocab_size, hidden_size, name (the embedding table), scale, add_embedding, vector, rows, row."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.vocab, self.hidden = int(p["vocab_size"]), int(p["hidden_size"])
+        self.name = self.prefix + p.get("name", "embed_tokens.weight")
+        self.scale = float(p.get("scale", 1.0))
+        self.add_embedding = bool(p.get("add_embedding", True))
+        self.vector = None if p.get("vector") is None else self.prefix + str(p["vector"])
+        self.rows, self.row = int(p.get("rows", 1)), int(p.get("row", 0))
+        if self.vector is not None and not 0 <= self.row < self.rows:
+            raise ValueError(f"stream step '{self.vector}': row {self.row} of {self.rows}")
+        self.table = self.vec = None
+
+    def tensors(self):
+        out = [TensorSpec(self.name, (self.vocab, self.hidden), MATRIX)] if self.add_embedding else []
+        if self.vector is not None:
+            out.append(TensorSpec(self.vector, (self.rows, self.hidden), VECTOR))
+        return out
+
+    def bind(self, weights):
+        if self.add_embedding:
+            self.table = weights[self.name]
+        if self.vector is not None:
+            self.vec = weights[self.vector][self.row].to(torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ("elementwise",)
+
+    def forward(self, h, ctx):
+        if self.add_embedding or self.vec is not None:
+            ops.embed_add(h, ctx.token_ids if self.add_embedding else None, self.table, self.scale, self.vec)
 
 
 class OutputHead(Part):
@@ -70,3 +110,4 @@ class OutputHead(Part):
 
 register_embedding("token", TokenEmbedding)
 register_head("linear", OutputHead)
+register_stream_step("reinject_embedding", EmbeddingReinjection)

@@ -24,7 +24,7 @@ import os
 import torch
 
 from ..kernels import ops
-from .base import NormedSum
+from .base import NormedSum, ScaledSum
 
 
 def kernel_modules(dtype: torch.dtype) -> tuple:
@@ -137,20 +137,25 @@ def settle(h: torch.Tensor, delta, norm=None):
     if isinstance(delta, NormedSum) and not (getattr(norm, "adds_normed_sums", False) and type(delta.norm) is type(norm)):
         delta.add_onto(h)
         return None
+    if isinstance(delta, ScaledSum) and not getattr(norm, "adds_scaled_sums", False):
+        delta.add_onto(h)
+        return None
     return delta
 
 
-def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) for the stacked weight [2F, K] -> [M, F] in ``out_dtype``.  ``interleave`` 0: gate rows
+def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0,
+                  activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) for the stacked weight [2F, K] -> [M, F] in ``out_dtype``; ``activation`` is one of
+    ``ops.GATE_ACTIVATIONS`` (the products with a fused epilogue have the SiLU only).  ``interleave`` 0: gate rows
     first; ``ops.GATE_UP_GROUP``: gate and up rows interleaved in groups of that many features, which lets the products
     with a fused epilogue find a feature's gate and up in one thread."""
-    if interleave == ops.GATE_UP_GROUP and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
+    if activation == "silu" and interleave == ops.GATE_UP_GROUP and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
         if x.shape[0] <= ops.STREAM_M and x.shape[1] % 8 == 0:
             if _few_rows(x.shape[0], weight_gate_up):
                 return _stream(x, weight_gate_up, None, "swiglu")
         if x.shape[0] >= TC_SWIGLU_MIN_ROWS and x.shape[1] >= TC_SWIGLU_MIN_INNER and x.shape[1] % 8 == 0:
             return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
-    return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave)
+    return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave, activation)
 
 
 def linear_act(x: torch.Tensor, weight: torch.Tensor, bias, activation: str, out_dtype: torch.dtype, params=None) -> torch.Tensor:

@@ -11,7 +11,8 @@ from .registry import register_feed_forward
 
 
 class GatedMLP(FeedForward):
-    """params: hidden_size, intermediate_size, names (optional overrides)."""
+    """params: hidden_size, intermediate_size, activation (on the gate: one of ``ops.GATE_ACTIVATIONS``, default "silu"),
+    names (optional overrides)."""
 
     NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
 
@@ -19,6 +20,10 @@ class GatedMLP(FeedForward):
         super().__init__(spec, runtime)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        self.activation = str(spec.params.get("activation", "silu"))
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"feed-forward '{self.prefix}': unknown gate activation '{self.activation}'; known: "
+                             f"{', '.join(ops.GATE_ACTIVATIONS)}")
         self.names = {**self.NAMES, **dict(spec.params.get("names", {}))}
         self.w_gate_up = self.w_down = None
         self.interleave = 0
@@ -48,7 +53,7 @@ class GatedMLP(FeedForward):
     adds_to_residual = True
 
     def forward(self, x, ctx, residual=None):
-        act = linear_swiglu(x, self.w_gate_up, self.runtime.dtype, self.interleave)
+        act = linear_swiglu(x, self.w_gate_up, self.runtime.dtype, self.interleave, self.activation)
         if residual is not None:
             return linear_onto(act, self.w_down, residual)  # None: the residual sum was made in the product's epilogue
         return linear(act, self.w_down)

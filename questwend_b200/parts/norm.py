@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.manifest import NORM_WEIGHT, VECTOR, TensorSpec
-from .base import Norm, NormedSum
+from .base import Norm, NormedSum, ScaledSum
 from .registry import register_norm
 
 
@@ -30,8 +30,12 @@ class RMSNorm(Norm):
         return ("elementwise",)
 
     adds_split_sums = True      # ``delta`` may be a SplitSum: the kernel adds its planes
+    adds_scaled_sums = True     # ... or a ScaledSum: the kernel multiplies as it adds
 
     def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None):
+        if isinstance(delta, ScaledSum):
+            return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.runtime.dtype, delta=delta.y,
+                               write_sum=write_sum, rows=rows, delta_scale=delta.scale)
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.runtime.dtype, delta=delta,
                            write_sum=write_sum, rows=rows)
 

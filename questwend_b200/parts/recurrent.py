@@ -1,6 +1,6 @@
 """Mixers that carry a state of fixed size from token to token instead of keys and values: the state-space
-recurrence of Mamba-2, the gated delta rule with a decay per key channel, and the recurrent block around a real-gated
-linear recurrent unit (one number of state per channel).  All keep, per sequence, a 32-bit
+recurrence of Mamba-2, the gated delta rule with a decay per key channel, gated linear attention (the same decay, a plain
+outer-product write), and the recurrent block around a real-gated linear recurrent unit (one number of state per channel).  All keep, per sequence, a 32-bit
 state matrix per head and the last inputs of a short causal convolution, in the cache's per-slot state rows; a
 prompt and a single token run through the same kernels (``csrc/recurrent.cu``).  The projections are matrix
 products in the engine's dtype with 32-bit results; everything between them is 32-bit.
@@ -230,6 +230,72 @@ class RGLRUMixer(Mixer):
         return linear(g, self.w_out)
 
 
+class GatedLinearAttentionMixer(Mixer):
+    """Linear attention with a decay per head and key channel.  q = W_q h * ``q_scale`` and k = W_k h (heads x key_dim),
+    v = W_v h (heads x vdim); the decay is alpha = sigmoid(z)^(1 / ``tau``) with z = W_a2 (W_a1 h) + b (a low-rank
+    projection, heads x key_dim).  Per head S <- diag(alpha) S + k v^T from S = 0 and o = S^T q; each head's o is
+    RMS-normed over vdim with one weight shared by the heads, multiplied by silu(W_g h), and projected by W_o.  The
+    state, the decays (formed as exp(log_sigmoid(z) / tau)) and the norm are 32-bit.
+
+    params: hidden_size, heads, key_dim, vdim, decay_rank, tau, norm_eps, q_scale (default key_dim^-1/2), names (optional
+    overrides).  State per sequence: S, stored [heads, vdim, key_dim]."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "decay_down": "a1", "decay_up": "a2", "decay_bias": "a2.b",
+             "norm": "norm", "out": "o"}
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.key_dim, self.vdim = int(p["heads"]), int(p["key_dim"]), int(p["vdim"])
+        self.decay_rank = int(p["decay_rank"])
+        self.tau, self.eps = float(p["tau"]), float(p["norm_eps"])
+        self.q_scale = float(p.get("q_scale", self.key_dim ** -0.5))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        refusal = state_matrix_refusal(self.key_dim, self.vdim)
+        if refusal:
+            raise ValueError(f"gated linear attention '{self.prefix}': {refusal}")
+        if not self.tau > 0:
+            raise ValueError(f"gated linear attention '{self.prefix}': tau must be positive, got {self.tau}")
+        self.n_qk = self.heads * self.key_dim
+        self.n_v = self.heads * self.vdim
+
+    def tensors(self):
+        n, px, D = self.names, self.prefix, self.hidden
+        return [TensorSpec(px + n["q"], (self.n_qk, D), MATRIX), TensorSpec(px + n["k"], (self.n_qk, D), MATRIX),
+                TensorSpec(px + n["v"], (self.n_v, D), MATRIX), TensorSpec(px + n["gate"], (self.n_v, D), MATRIX),
+                TensorSpec(px + n["out"], (D, self.n_v), MATRIX),
+                TensorSpec(px + n["norm"], (self.vdim,), VECTOR, NORM_WEIGHT),
+                TensorSpec(px + n["decay_down"], (self.decay_rank, D), MATRIX),
+                TensorSpec(px + n["decay_up"], (self.n_qk, self.decay_rank), MATRIX),
+                TensorSpec(px + n["decay_bias"], (self.n_qk,), VECTOR)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        # one projection for everything that reads the stream: q | k | v | gate | decay latent
+        self.w_in = torch.cat([take_weight(weights, px + n[k]) for k in ("q", "k", "v", "gate", "decay_down")], dim=0).contiguous()
+        self.w_decay_up, self.w_out = weights[px + n["decay_up"]], weights[px + n["out"]]
+        self.decay_bias, self.norm_w = _f32(weights, px + n["decay_bias"]), _f32(weights, px + n["norm"])
+
+    def kernel_modules(self):
+        return ("recurrent", "elementwise", *linear_modules(self.runtime.dtype))
+
+    def state_spec(self):
+        return StateSpec((self.heads, self.vdim, self.key_dim), torch.float32)       # column by column
+
+    def forward(self, x, ctx, cache):
+        dtype = self.runtime.dtype
+        n_qkv = 2 * self.n_qk + self.n_v
+        proj = linear(x, self.w_in)
+        a_raw = linear(ops.bias_act(proj, None, "none", dtype, n_qkv + self.n_v, self.decay_rank), self.w_decay_up)
+        o = ops.gla_scan(proj, a_raw, self.decay_bias, cache.state, ctx, self.heads, self.key_dim, self.vdim, self.q_scale,
+                         self.tau, write_state=cache.writable)
+        g = ops.gated_part_norm(o, proj, n_qkv, self.norm_w, self.heads, self.eps, gate_first=False, out_dtype=dtype,
+                                gate_activation="silu")
+        return linear(g, self.w_out)
+
+
 register_mixer("mamba2", Mamba2Mixer)
 register_mixer("rglru", RGLRUMixer)
 register_mixer("gated_delta_channelwise", GatedDeltaMixer)
+register_mixer("gated_linear_attention", GatedLinearAttentionMixer)

@@ -4,7 +4,7 @@ from __future__ import annotations
 from .base import PartSpec, Runtime
 
 _REGISTRIES: dict[str, dict[str, type]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {}, "stream_step": {},
 }
 
 
@@ -42,6 +42,10 @@ def register_embedding(kind, cls, replace=False):
 
 def register_head(kind, cls, replace=False):
     return _register("head", kind, cls, replace)
+
+
+def register_stream_step(kind, cls, replace=False):
+    return _register("stream_step", kind, cls, replace)
 
 
 def kinds(family: str) -> list[str]:

@@ -83,5 +83,51 @@ class PairedRotaryEncoding(PositionEncoding):
         return ctx.shared[key]
 
 
+def wavelength_scaled_frequencies(rotary_dim: int, theta: float, factor: float, low: float, high: float, original: float):
+    """Angle per position of each pair, in float64, scaled by wavelength: with f_i = theta^(-2i/n) and wavelength
+    l = 2 pi / f, a pair keeps f where l < original / high, turns by f / factor where l > original / low, and between the
+    two by (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    import math
+    i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    f = theta ** (-2.0 * i / rotary_dim)
+    wavelength = 2.0 * math.pi / f
+    s = (original / wavelength - low) / (high - low)
+    mixed = (1.0 - s) * f / factor + s * f
+    return torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, mixed))
+
+
+class WavelengthScaledRotary(PositionEncoding):
+    """Rotation angles theta^(-2i/n), optionally scaled by wavelength for contexts longer than the ``original`` one.
+    params: theta, rotary_dim, and for the scaling (all four or none) factor, low, high, original.  ``prepare`` gives cos
+    and sin [T, rotary_dim / 2]; which values are paired is the business of the kernel that applies them."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.theta = float(p["theta"])
+        self.rotary_dim = int(p["rotary_dim"])
+        if self.rotary_dim <= 0 or self.rotary_dim % 2:
+            raise ValueError(f"rotary size {self.rotary_dim} must be positive and even")
+        scaling = [p.get(k) for k in ("factor", "low", "high", "original")]
+        if any(v is None for v in scaling) and not all(v is None for v in scaling):
+            raise ValueError("a rotation scaled by wavelength needs all of factor, low, high and original")
+        if scaling[0] is None:
+            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            freqs = self.theta ** (-2.0 * i / self.rotary_dim)
+        else:
+            freqs = wavelength_scaled_frequencies(self.rotary_dim, self.theta, *[float(v) for v in scaling])
+        self.inv_freq = freqs.to(runtime.device)
+
+    def kernel_modules(self):
+        return ("rope_kv",)
+
+    def prepare(self, ctx):
+        key = ("rotary_wavelength", id(self))
+        if key not in ctx.shared:
+            ctx.shared[key] = ops.rope_table(ctx.tok_pos, self.inv_freq)
+        return ctx.shared[key]
+
+
 register_position("rotary_neox", RotaryEncoding)
 register_position("rotary_pairs", PairedRotaryEncoding)
+register_position("rotary_wavelength", WavelengthScaledRotary)
