@@ -13,7 +13,7 @@
 //
 //   maps_prep         bias, per-map RMS norm of q and k (a weight of dim values shared by heads and maps), rotation of the
 //                     first rdims values of every map of q and k, cache write of a step's tokens; q out
-//   maps_prefill      any number of new tokens per sequence (float and bfloat16, any sizes that are multiples of 8)
+//   maps_prefill      any number of new tokens per sequence (float and bfloat16, any sizes up to 256)
 //   maps_prefill_mma  bfloat16 prompts on the tensor cores
 //   maps_decode       one new token per sequence: runs of pages, one block of threads a run, then maps_merge, which also
 //                     takes the difference and the norm
@@ -92,11 +92,12 @@ __global__ void maps_prep_kernel(const float* __restrict__ qkv, const float* __r
     for (int i = lane; i < n; i += 32) dst[i] = from_f32<T>(rd > 0 ? maps_turned(buf, i, rd, cs, sn, interleaved) : buf[i]);
 }
 
-static int check_maps_sizes(const char* what, int H, int G, int maps, int dim, int vdim, int table_width, int chunk) {
+// `step`: 1 for the kernels that read value by value, 8 for those that copy 16 bytes at a time
+static int check_maps_sizes(const char* what, int H, int G, int maps, int dim, int vdim, int table_width, int chunk, int step) {
     if (H <= 0 || G <= 0 || H % G) return qwb_fail(QWB_ERR_ARG, "%s: %d query heads are not a multiple of %d key/value heads", what, H, G);
     if (maps < 1 || maps > QWB_MAPS_MAX) return qwb_fail(QWB_ERR_ARG, "%s: %d score maps per head (1 or 2)", what, maps);
-    if (dim <= 0 || dim % 8 || dim > QWB_MAPS_MAX_DIM || vdim <= 0 || vdim % 8 || vdim > QWB_MAPS_MAX_DIM)
-        return qwb_fail(QWB_ERR_ARG, "%s: key size %d or value size %d is not a multiple of 8 in [8, %d]", what, dim, vdim, QWB_MAPS_MAX_DIM);
+    if (dim <= 0 || dim % step || dim > QWB_MAPS_MAX_DIM || vdim <= 0 || vdim % step || vdim > QWB_MAPS_MAX_DIM)
+        return qwb_fail(QWB_ERR_ARG, "%s: key size %d or value size %d is not a multiple of %d in [%d, %d]", what, dim, vdim, step, step, QWB_MAPS_MAX_DIM);
     if (table_width <= 0 || chunk < 0) return qwb_fail(QWB_ERR_ARG, "%s: bad table width %d or chunk %d", what, table_width, chunk);
     return 0;
 }
@@ -106,7 +107,7 @@ extern "C" int qwb_maps_prep(const float* qkv, const float* bias, const float* q
                              void* v_pool, int dtype, int T, int H, int G, int maps, int dim, int vdim, int rdims, int interleaved,
                              float eps, int store_kv, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (int rc = check_maps_sizes("maps_prep", H, G, maps, dim, vdim, table_width, 0)) return rc;
+    if (int rc = check_maps_sizes("maps_prep", H, G, maps, dim, vdim, table_width, 0, 1)) return rc;
     if (rdims < 0 || rdims > dim || rdims % 2) return qwb_fail(QWB_ERR_ARG, "maps_prep: a rotation of %d of %d values", rdims, dim);
     if (rdims > 0 && (!cos_t || !sin_t)) return qwb_fail(QWB_ERR_ARG, "maps_prep: a rotation without its table");
     dim3 grid(T, ((H + G) * maps + G + 3) / 4);
@@ -282,7 +283,7 @@ extern "C" int qwb_maps_prefill(const void* q, const void* k_pool, const void* v
                                 int table_width, float scale, float softcap, int chunk, float lambda, int norm_out, float eps,
                                 float out_scale, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
-    if (int rc = check_maps_sizes("maps_prefill", H, G, maps, dim, vdim, table_width, chunk)) return rc;
+    if (int rc = check_maps_sizes("maps_prefill", H, G, maps, dim, vdim, table_width, chunk, 1)) return rc;
     if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "maps_prefill: batch %d or heads %d above 65535", B, H);
     if (dtype == QWB_DT_F32)
         return launch_maps_prefill<float>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, H, G, maps, dim, vdim, table_width,
@@ -548,7 +549,7 @@ extern "C" int qwb_maps_decode(const void* q, const void* k_pool, const void* v_
                                float scale, float softcap, int chunk, int n_runs, float lambda, int norm_out, float eps, float out_scale,
                                cudaStream_t stream) {
     if (B <= 0) return 0;
-    if (int rc = check_maps_sizes("maps_decode", H, G, maps, dim, vdim, table_width, chunk)) return rc;
+    if (int rc = check_maps_sizes("maps_decode", H, G, maps, dim, vdim, table_width, chunk, 8)) return rc;
     if (n_runs <= 0 || n_runs > 65535 || B > 65535) return qwb_fail(QWB_ERR_ARG, "maps_decode: %d runs, %d sequences", n_runs, B);
     if (dtype == QWB_DT_F32)
         return launch_maps_decode<float>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, H, G, maps, dim, vdim, table_width, scale,

@@ -59,16 +59,15 @@ def pool_attention_refusal(dim: int, vdim: int) -> str | None:
     return None
 
 
-MAPS_ATTN_DIM_STEP = 8      # the attention with score maps takes key and value sizes that are multiples of this ...
-MAPS_ATTN_MAX_DIM = 256     # ... up to this (csrc/attention_maps.cu: QWB_MAPS_MAX_DIM)
-MAPS_ATTN_MAX_MAPS = 2      # ... and this many score maps per head (QWB_MAPS_MAX)
+MAPS_ATTN_MAX_DIM = 256     # the attention with score maps takes key and value sizes up to this (csrc/attention_maps.cu:
+MAPS_ATTN_MAX_MAPS = 2      # QWB_MAPS_MAX_DIM) and this many score maps per head (QWB_MAPS_MAX)
+MAPS_ATTN_FAST_STEP = 8     # sizes that are multiples of this take the kernels that copy 16 bytes at a time; others the plain one
 
 
 def maps_attention_refusal(maps: int, dim: int, vdim: int) -> str | None:
     if not 1 <= maps <= MAPS_ATTN_MAX_MAPS:
         return f"the attention with score maps takes 1 or {MAPS_ATTN_MAX_MAPS} maps per head, not {maps}"
     for what, n in (("key", dim), ("value", vdim)):
-        if n <= 0 or n % MAPS_ATTN_DIM_STEP or n > MAPS_ATTN_MAX_DIM:
-            return (f"the attention with score maps takes {what} sizes that are multiples of {MAPS_ATTN_DIM_STEP} up to "
-                    f"{MAPS_ATTN_MAX_DIM}, not {n}")
+        if n <= 0 or n > MAPS_ATTN_MAX_DIM:
+            return f"the attention with score maps takes {what} sizes up to {MAPS_ATTN_MAX_DIM}, not {n}"
     return None

@@ -1039,8 +1039,8 @@ def pool_attention(q: torch.Tensor, k_pool, v_pool, pk_pool, pv_pool, page_table
                    scale: float, window: int, pool: int, interleaved: bool, impl: str = "auto") -> torch.Tensor:
     """Attention of a step's tokens over their window and the block rows before it.  ``q`` [T, H, dim] in the cache's
     dtype; returns [T, H * vdim] in that dtype, each head turned back by the query's position if ``cos_v`` is given.
-    Steps of one token per sequence take the kernel that cuts the keys into runs; other steps the tensor-core kernel
-    where it fits (``impl`` "auto" or "mma"), else the plain one ("plain")."""
+    Steps of one token per sequence take the kernel that cuts the keys into runs (sizes that are multiples of 8); other
+    steps the tensor-core kernel where it fits (``impl`` "auto" or "mma"), else the plain one ("plain")."""
     _need(q, "q", k_pool.dtype, 3)
     T, H, dim = q.shape
     G, vdim = k_pool.shape[1], v_pool.shape[3]
@@ -1076,6 +1076,8 @@ def pool_attention(q: torch.Tensor, k_pool, v_pool, pk_pool, pv_pool, page_table
 # ----------------------------------------------------------------------------- attention with score maps
 MAPS_MAX_DIM = 256          # csrc/attention_maps.cu: QWB_MAPS_MAX_DIM
 MAPS_MAX = 2                # ... QWB_MAPS_MAX: score maps per head
+MAPS_PREFILL_MMA = False
+MAPS_FAST_STEP = 8          # key and value sizes that are multiples of this take the kernels that copy 16 bytes at a time
 
 
 def maps_prep(qkv: torch.Tensor, bias, q_weight, k_weight, cos, sin, ctx, page_table, k_pool, v_pool, n_heads: int,
@@ -1114,7 +1116,7 @@ def maps_prep(qkv: torch.Tensor, bias, q_weight, k_weight, cos, sin, ctx, page_t
 
 def maps_prefill_mma_fits(dtype: torch.dtype, maps: int, dim: int, vdim: int) -> bool:
     """Whether prompts take the tensor-core kernel: bfloat16, keys in multiples of 16, values of 8, tiles that fit."""
-    if dtype != torch.bfloat16:
+    if dtype != torch.bfloat16 or not MAPS_PREFILL_MMA:
         return False
     return bool(_lookup("attention_maps", "qwb_maps_prefill_mma_fits")[1](_i(DT_BF16), _i(maps), _i(dim), _i(vdim)))
 
@@ -1126,8 +1128,8 @@ def maps_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, maps: int, 
     the cache's dtype; returns [T, H * vdim] in that dtype: map 0's output, minus ``lam`` times map 1's if there are two,
     then (``norm_out``) divided by its root mean square over vdim and multiplied by ``out_scale``.  Scores are scaled,
     soft-capped (``softcap`` > 0) and masked causally, and to the query's chunk of ``chunk`` positions if that is > 0.
-    Steps of one token per sequence take the kernel that cuts the keys into runs; other steps the tensor-core kernel
-    where it fits (``impl`` "auto" or "mma"), else the plain one ("plain")."""
+    Steps of one token per sequence take the kernel that cuts the keys into runs (sizes that are multiples of 8); other
+    steps the tensor-core kernel where it fits (``impl`` "auto" or "mma"), else the plain one ("plain")."""
     _need(q, "q", k_pool.dtype, 3)
     T, H, kdim = q.shape
     G, vdim = k_pool.shape[1], v_pool.shape[3]
@@ -1136,7 +1138,7 @@ def maps_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, maps: int, 
     dim = kdim // maps
     out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
     width = page_table.shape[1]
-    if ctx.single_token:
+    if ctx.single_token and dim % MAPS_FAST_STEP == 0 and vdim % MAPS_FAST_STEP == 0:
         lib = _lookup("attention_maps", "qwb_maps_decode_runs")[0]
         n_runs = lib.qwb_maps_decode_runs(_i(ctx.max_len), _i(chunk))
         lib.qwb_maps_decode_scratch_floats.restype = ctypes.c_longlong
