@@ -295,6 +295,297 @@ extern "C" int qwb_maps_prefill(const void* q, const void* k_pool, const void* v
 }
 
 // ---------------------------------------------------------------------------------
+// prefill on the tensor cores (bfloat16, mma.sync m16n8k16): block = 64 queries of one (sequence, query head), 4 warps of
+// 16 rows; keys in tiles of 64 = one page of the cache, from the page of the first key that the tile's first query sees
+// to the page of its last query.  The maps run one after the other over the same pages: map m reads columns
+// [m * dim, (m + 1) * dim) of the key rows and the same values.  Q, K and V tiles sit in shared memory with rows padded
+// by 16 bytes (conflict-free ldmatrix); K has two buffers, V one: the next tile's keys are copied in (cp.async) under
+// this tile's work, its values under its own scores and softmax.  Scores, the cap, maxima, sums, accumulators, the
+// difference of the maps and the norm are 32-bit; probabilities are rounded to bfloat16 for the second product.
+// dim a multiple of 16, vdim of 8.
+// ---------------------------------------------------------------------------------
+#define MM_BQ 64
+#define MM_BK 64
+#define MM_PAD 8
+
+__device__ __forceinline__ void mm_ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mm_ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mm_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 16 bytes from global to shared memory; `bytes` 0 writes zeros (src must still be a valid address)
+__device__ __forceinline__ void mm_cp16(bf16* dst, const bf16* src, int bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void mm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void mm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t mm_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// tanh(x) = 1 - 2 / (e^(2x) + 1): exact at both ends (e^(2x) = inf or 0), a few units of the last place in between
+__device__ __forceinline__ float mm_tanh(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+
+template <int NV, int MAPS>     // n-tiles of 8 value columns the accumulator has room for; score maps per head
+__global__ void __launch_bounds__(128)
+maps_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        const int* __restrict__ page_table, const int* __restrict__ cu_seqlens, const int* __restrict__ pos0,
+                        bf16* __restrict__ out, int H, int G, int dim, int vdim, int table_width, float scale, float softcap,
+                        int chunk, float lambda, int norm_out, float eps, float out_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int ldq = dim + MM_PAD, ldv = vdim + MM_PAD, kdim = MAPS * dim;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);           // [64][ldq]
+    bf16* Kbuf = Qs + MM_BQ * ldq;                          // [2][64][ldq]
+    bf16* Vbuf = Kbuf + 2 * MM_BK * ldq;                    // [64][ldv]
+
+    const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * MM_BQ;
+    const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+    if (q0 >= n) return;
+    const int g_kv = h / (H / G);
+    const int p0 = pos0[b];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nq = min(MM_BQ, n - q0);
+    const int gr = lane >> 2, tq = lane & 3;
+    const int pos_a = p0 + q0 + warp * 16 + gr, pos_b = pos_a + 8;  // positions of the thread's two rows
+    const int lo_a = maps_first_key(pos_a, chunk), lo_b = maps_first_key(pos_b, chunk);
+
+    const int k_hi = p0 + q0 + nq - 1;                              // last key any query of the tile sees
+    const int k_lo = maps_first_key(p0 + q0, chunk);                // first key any of them sees
+    const int nv_used = vdim / 8;
+    const int first_page = k_lo / MM_BK, n_tiles = k_hi / MM_BK - first_page + 1;
+    const int* pages = page_table + (size_t)b * table_width;
+    const int warp_lo = p0 + q0 + warp * 16, warp_hi = warp_lo + 15;
+    const int warp_first = maps_first_key(warp_hi, chunk);          // the first key that every row of the warp may see
+    const float log2e = 1.4426950408889634f;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const float mul_s = softcap > 0.f ? scale * inv_cap : scale * log2e;   // scores in units of ln 2: exp2f below
+    const float cap2 = softcap * log2e;
+
+    float res[MAPS > 1 ? NV : 1][4];                                // map 0's normed sums, until the difference is formed
+
+#pragma unroll
+    for (int mp = 0; mp < MAPS; ++mp) {
+        auto copy_keys = [&](int it, int stage) {                   // one commit group
+            const int page = first_page + it;
+            const int rows = min(MM_BK, k_hi + 1 - page * MM_BK);
+            const bf16* ks = k_pool + ((size_t)pages[page] * G + g_kv) * MM_BK * kdim + mp * dim;
+            bf16* Kd = Kbuf + stage * MM_BK * ldq;
+            for (int idx = tid; idx < MM_BK * (dim / 8); idx += blockDim.x) {
+                const int r = idx / (dim / 8), c = (idx - r * (dim / 8)) * 8;
+                mm_cp16(Kd + r * ldq + c, ks + (size_t)(r < rows ? r : 0) * kdim + c, r < rows ? 16 : 0);
+            }
+            mm_commit();
+        };
+        auto copy_values = [&](int it) {                            // one commit group
+            const int page = first_page + it;
+            const int rows = min(MM_BK, k_hi + 1 - page * MM_BK);
+            const bf16* vs = v_pool + ((size_t)pages[page] * G + g_kv) * MM_BK * vdim;
+            for (int idx = tid; idx < MM_BK * (vdim / 8); idx += blockDim.x) {
+                const int r = idx / (vdim / 8), c = (idx - r * (vdim / 8)) * 8;
+                mm_cp16(Vbuf + r * ldv + c, vs + (size_t)(r < rows ? r : 0) * vdim + c, r < rows ? 16 : 0);
+            }
+            mm_commit();
+        };
+        // this map's queries (the last readers of Qs, Kbuf and Vbuf passed the barrier that closed the map before)
+        for (int idx = tid; idx < MM_BQ * (dim / 8); idx += blockDim.x) {
+            const int r = idx / (dim / 8), c = (idx - r * (dim / 8)) * 8;
+            const bool in = r < nq;
+            mm_cp16(Qs + r * ldq + c, q + ((size_t)(t0 + (in ? q0 + r : 0)) * H + h) * kdim + mp * dim + c, in ? 16 : 0);
+        }
+        // groups in the order of their commits: [Q, K0], V0, K1, V1, K2, ...
+        copy_keys(0, 0);
+        copy_values(0);
+
+        float o[NV][4];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows gr and gr + 8 of the warp's 16
+
+        for (int it = 0; it < n_tiles; ++it) {
+            const bf16* Ks = Kbuf + (it & 1) * MM_BK * ldq;
+            const bf16* Vs = Vbuf;
+            const bool more = it + 1 < n_tiles;
+            if (more) {                                             // the next keys into the other buffer (its last readers
+                copy_keys(it + 1, (it + 1) & 1);                    // passed the barrier at the end of the round before)
+                mm_wait<2>();                                       // this tile's keys (and Q) are there
+            } else {
+                mm_wait<1>();
+            }
+            __syncthreads();
+            const int key0 = (first_page + it) * MM_BK;
+            // a tile that no row of the warp sees (behind its last row, or before its chunk) is skipped by the warp
+            const bool none = key0 > warp_hi || key0 + MM_BK <= maps_first_key(warp_lo, chunk);
+            float s[8][4];
+            if (!none) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                for (int d = 0; d < dim; d += 16) {
+                    uint32_t a0, a1, a2, a3;
+                    mm_ldsm_x4(a0, a1, a2, a3, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldq + d + (lane >> 4) * 8);
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {                // two tiles of 8 keys a load
+                        uint32_t b0, b1, b2, b3;
+                        mm_ldsm_x4(b0, b1, b2, b3, Ks + (j * 8 + (lane & 7) + (lane >> 4) * 8) * ldq + d + ((lane >> 3) & 1) * 8);
+                        mm_mma(s[j], a0, a1, a2, a3, b0, b1);
+                        mm_mma(s[j + 1], a0, a1, a2, a3, b2, b3);
+                    }
+                }
+                // a tile that every row of the warp sees whole needs no mask (most tiles of a long prompt)
+                const bool whole = key0 + MM_BK - 1 <= warp_lo && key0 >= warp_first;
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        bool ok = true;
+                        if (!whole) {
+                            const int key = key0 + j * 8 + tq * 2 + (e & 1);
+                            ok = key <= (e < 2 ? pos_a : pos_b) && key >= (e < 2 ? lo_a : lo_b) && key <= k_hi;
+                        }
+                        float v = s[j][e] * mul_s;
+                        if (softcap > 0.f) v = cap2 * mm_tanh(v);
+                        s[j][e] = ok ? v : -INFINITY;
+                    }
+                    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                    mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+                }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+                const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+                const float alpha0 = exp2f(m0 - base0), alpha1 = exp2f(m1 - base1);    // m = -inf gives 0
+                float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    s[j][0] = exp2f(s[j][0] - base0); s[j][1] = exp2f(s[j][1] - base0);
+                    s[j][2] = exp2f(s[j][2] - base1); s[j][3] = exp2f(s[j][3] - base1);
+                    sum0 += s[j][0] + s[j][1];
+                    sum1 += s[j][2] + s[j][3];
+                }
+                sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+                sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+                l0 = l0 * alpha0 + sum0; l1 = l1 * alpha1 + sum1;
+                m0 = mn0; m1 = mn1;
+#pragma unroll
+                for (int j = 0; j < NV; ++j) { o[j][0] *= alpha0; o[j][1] *= alpha0; o[j][2] *= alpha1; o[j][3] *= alpha1; }
+            }
+
+            if (more) mm_wait<1>(); else mm_wait<0>();              // this tile's values are there
+            __syncthreads();
+            if (!none) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {                    // O += P V, 16 keys a step
+                    const uint32_t a0 = mm_pack(s[2 * ks][0], s[2 * ks][1]), a1 = mm_pack(s[2 * ks][2], s[2 * ks][3]);
+                    const uint32_t a2 = mm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), a3 = mm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+                    for (int j = 0; j < NV; j += 2) {
+                        if (j < nv_used) {                          // vdim / 8 may be odd: the second tile of a pair reads padding
+                            uint32_t b0, b1, b2, b3;                // or the next row's start, and its result is never stored
+                            mm_ldsm_x4_trans(b0, b1, b2, b3, Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + j * 8 + (lane >> 4) * 8);
+                            mm_mma(o[j], a0, a1, a2, a3, b0, b1);
+                            if (j + 1 < NV) mm_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
+                        }
+                    }
+                }
+            }
+            __syncthreads();                                        // the values' buffer may be copied into again
+            if (more) copy_values(it + 1);
+        }
+
+        const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        if (MAPS > 1 && mp == 0) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                res[MAPS > 1 ? j : 0][0] = o[j][0] * inv0; res[MAPS > 1 ? j : 0][1] = o[j][1] * inv0;
+                res[MAPS > 1 ? j : 0][2] = o[j][2] * inv1; res[MAPS > 1 ? j : 0][3] = o[j][3] * inv1;
+            }
+        } else {
+            float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                o[j][0] *= inv0; o[j][1] *= inv0; o[j][2] *= inv1; o[j][3] *= inv1;
+                if (MAPS > 1) {
+                    o[j][0] = res[MAPS > 1 ? j : 0][0] - lambda * o[j][0]; o[j][1] = res[MAPS > 1 ? j : 0][1] - lambda * o[j][1];
+                    o[j][2] = res[MAPS > 1 ? j : 0][2] - lambda * o[j][2]; o[j][3] = res[MAPS > 1 ? j : 0][3] - lambda * o[j][3];
+                }
+                if (j < nv_used) { ss0 += o[j][0] * o[j][0] + o[j][1] * o[j][1]; ss1 += o[j][2] * o[j][2] + o[j][3] * o[j][3]; }
+            }
+            float mul0 = 1.f, mul1 = 1.f;
+            if (norm_out) {
+                ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+                ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+                mul0 = rsqrtf(ss0 / (float)vdim + eps) * out_scale;
+                mul1 = rsqrtf(ss1 / (float)vdim + eps) * out_scale;
+            }
+            const int row_a = warp * 16 + gr, row_b = row_a + 8;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                if (j < nv_used) {
+                    const int col = j * 8 + tq * 2;
+                    if (row_a < nq) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + q0 + row_a) * H + h) * vdim + col) = mm_pack(o[j][0] * mul0, o[j][1] * mul0);
+                    if (row_b < nq) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + q0 + row_b) * H + h) * vdim + col) = mm_pack(o[j][2] * mul1, o[j][3] * mul1);
+                }
+            }
+        }
+    }
+}
+
+// Q and two key buffers [64][dim + 8] and one value buffer [64][vdim + 8] of bfloat16
+static size_t mm_smem_bytes(int dim, int vdim) {
+    return ((size_t)3 * MM_BK * (dim + MM_PAD) + (size_t)MM_BK * (vdim + MM_PAD)) * sizeof(bf16);
+}
+
+extern "C" int qwb_maps_prefill_mma_fits(int dtype, int maps, int dim, int vdim) {
+    return dtype == QWB_DT_BF16 && maps >= 1 && maps <= QWB_MAPS_MAX && dim > 0 && dim % 16 == 0 && vdim > 0 && vdim % 8 == 0 &&
+           dim <= QWB_MAPS_MAX_DIM && vdim <= QWB_MAPS_MAX_DIM && mm_smem_bytes(dim, vdim) <= 220 * 1024;
+}
+
+// q [T, H, maps * dim] bfloat16; out [T, H * vdim] bfloat16.
+extern "C" int qwb_maps_prefill_mma(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
+                                    const int* pos0, void* out, int B, int max_new, int H, int G, int maps, int dim, int vdim,
+                                    int table_width, float scale, float softcap, int chunk, float lambda, int norm_out, float eps,
+                                    float out_scale, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    if (int rc = check_maps_sizes("maps_prefill_mma", H, G, maps, dim, vdim, table_width, chunk, 8)) return rc;
+    if (!qwb_maps_prefill_mma_fits(QWB_DT_BF16, maps, dim, vdim))
+        return qwb_fail(QWB_ERR_ARG, "maps_prefill_mma: keys of %d (a multiple of 16) and values of %d (of 8) that fit in shared memory", dim, vdim);
+    if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "maps_prefill_mma: batch %d or heads %d above 65535", B, H);
+    for (const void* p : {q, k_pool, v_pool, (const void*)out})
+        if ((uintptr_t)p % 16) return qwb_fail(QWB_ERR_ARG, "maps_prefill_mma: a tensor is not 16-byte aligned");
+    const size_t smem = mm_smem_bytes(dim, vdim);
+    const dim3 grid((max_new + MM_BQ - 1) / MM_BQ, H, B);
+#define QWB_MM(NV, MAPS)                                                                                                        \
+    do {                                                                                                                        \
+        if (smem > 48 * 1024) {                                                                                                 \
+            cudaError_t e = cudaFuncSetAttribute(maps_prefill_mma_kernel<NV, MAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "maps_prefill_mma: %s", cudaGetErrorString(e));                 \
+        }                                                                                                                       \
+        qwb_launch(maps_prefill_mma_kernel<NV, MAPS>, grid, 128, smem, stream, (const bf16*)q, (const bf16*)k_pool,             \
+                   (const bf16*)v_pool, page_table, cu_seqlens, pos0, (bf16*)out, H, G, dim, vdim, table_width, scale, softcap, \
+                   chunk, lambda, norm_out, eps, out_scale);                                                                    \
+    } while (0)
+#define QWB_MM_SIZES(MAPS)                                                                                                      \
+    do {                                                                                                                        \
+        if (vdim <= 32) QWB_MM(4, MAPS); else if (vdim <= 64) QWB_MM(8, MAPS); else if (vdim <= 128) QWB_MM(16, MAPS);          \
+        else QWB_MM(32, MAPS);                                                                                                  \
+    } while (0)
+    if (maps == 1) QWB_MM_SIZES(1); else QWB_MM_SIZES(2);
+#undef QWB_MM_SIZES
+#undef QWB_MM
+    return qwb_check_launch("maps_prefill_mma");
+}
+
+// ---------------------------------------------------------------------------------
 // decode: one new token per sequence (its position is len - 1).  The keys it sees, first .. len - 1 with first the start
 // of its chunk (or 0), are cut into runs of whole pages counted from the page of the first key: 2 pages a run, doubled
 // while that would give more than 16 runs.  Which keys a run holds follows from the sequence's own length alone.

@@ -1076,7 +1076,7 @@ def pool_attention(q: torch.Tensor, k_pool, v_pool, pk_pool, pv_pool, page_table
 # ----------------------------------------------------------------------------- attention with score maps
 MAPS_MAX_DIM = 256          # csrc/attention_maps.cu: QWB_MAPS_MAX_DIM
 MAPS_MAX = 2                # ... QWB_MAPS_MAX: score maps per head
-MAPS_PREFILL_MMA = False
+MAPS_PREFILL_MMA = True     # bfloat16 prompts take the tensor-core kernel where it fits; False: always the plain one
 MAPS_FAST_STEP = 8          # key and value sizes that are multiples of this take the kernels that copy 16 bytes at a time
 
 

@@ -310,6 +310,84 @@ def test_a_far_key_among_hundreds_and_the_first_tokens():
         assert close(run_mixer(part, dtype, [x], plan)[0], ref, dtype), plan[0]
 
 
+# ----------------------------------------------------------------------------- the prompt kernel on the tensor cores
+def maps_oracle(q, k, v, pos0, maps, scale, softcap, chunk, lam, norm_out, eps, out_scale, H, G):
+    """q [n, H, maps, dim], k [L, G, maps, dim], v [L, G, vdim] of one sequence (float64); the n queries sit at
+    pos0 .. pos0 + n - 1.  Returns [n, H * vdim]."""
+    n, L = q.shape[0], k.shape[0]
+    out = np.zeros((n, H, v.shape[2]))
+    for h in range(H):
+        g = h // (H // G)
+        maps_out = []
+        for m in range(maps):
+            s = q[:, h, m] @ k[:, g, m].T * scale
+            if softcap > 0:
+                s = softcap * np.tanh(s / softcap)
+            i, j = np.arange(pos0, pos0 + n)[:, None], np.arange(L)[None, :]
+            seen = (j <= i) & ((i // chunk == j // chunk) if chunk > 0 else True)
+            s = np.where(seen, s, -np.inf)
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            maps_out.append((p / p.sum(axis=1, keepdims=True)) @ v[:, g])
+        o = maps_out[0] - (lam * maps_out[1] if maps == 2 else 0.0)
+        if norm_out:
+            o = o / np.sqrt((o ** 2).mean(axis=1, keepdims=True) + eps) * out_scale
+        out[:, h] = o
+    return out.reshape(n, -1)
+
+
+@pytest.mark.parametrize("maps, H, G, dim, vdim, chunk, softcap", [
+    (2, 4, 2, 16, 32, 0, 3.0), (1, 6, 3, 32, 24, 70, 0.0), (2, 2, 1, 64, 128, 0, 0.0), (1, 2, 2, 128, 64, 64, 0.0),
+    (1, 3, 1, 48, 8, 130, 2.0), (2, 2, 2, 32, 136, 200, 5.0), (1, 1, 1, 16, 16, 1, 0.0), (2, 8, 2, 16, 40, 5, 0.0)])
+def test_tensor_core_prompt_kernel(maps, H, G, dim, vdim, chunk, softcap):
+    """Sequences of unequal lengths with prompts that go on from cached tokens (positions that are not multiples of the
+    tile), pages in a shuffled order; a key with a large score sits at the first position a query sees, at the one before
+    it, at position 0 and at page borders.  Against float64 attention on the same bfloat16 inputs and against the plain
+    kernel."""
+    from types import SimpleNamespace
+    assert ops.maps_prefill_mma_fits(torch.bfloat16, maps, dim, vdim)
+    rng = np.random.default_rng(dim + vdim + chunk)
+    before, new = [0, 37, 200, 64, 5], [150, 91, 130, 1, 64]
+    B, lam, eps, out_scale, scale = len(new), 0.35, 1e-5, 0.6, dim ** -0.5
+    total = [a + b for a, b in zip(before, new)]
+    width = max((t + 63) // 64 for t in total)
+    order = rng.permutation(B * width + 3)
+    table = np.zeros((B, width), dtype=np.int32)
+    k_pool = torch.zeros((len(order), G, 64, maps * dim), dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.zeros((len(order), G, 64, vdim), dtype=torch.bfloat16, device=DEV)
+    qs, ks, vs = [], [], []
+    for b in range(B):
+        L = total[b]
+        k = pp.round_bf16(rng.standard_normal((L, G, maps, dim)))
+        v = pp.round_bf16(rng.standard_normal((L, G, vdim)))
+        q = pp.round_bf16(rng.standard_normal((new[b], H, maps, dim)))
+        for i in range(0, new[b], 7):       # a key that stands out: at the edge of what query i sees, or just past it
+            pos = before[b] + i
+            first = (pos // chunk) * chunk if chunk > 0 else 0
+            for j in (first, first - 1, 0, 64 * (pos // 64), 64 * (pos // 64) - 1)[i % 5:i % 5 + 1]:
+                if 0 <= j < L:
+                    k[j] = pp.round_bf16(3.0 * q[i, ::H // G] / np.sqrt(scale * dim))
+        table[b, :(L + 63) // 64] = order[b * width:b * width + (L + 63) // 64]
+        for page in range((L + 63) // 64):
+            rows = slice(64 * page, min(64 * page + 64, L))
+            k_pool[table[b, page], :, :rows.stop - rows.start] = dev(k[rows].reshape(-1, G, maps * dim).transpose(1, 0, 2), torch.bfloat16)
+            v_pool[table[b, page], :, :rows.stop - rows.start] = dev(v[rows].transpose(1, 0, 2), torch.bfloat16)
+        qs.append(q), ks.append(k), vs.append(v)
+    cu = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    ctx = SimpleNamespace(single_token=False, n_seqs=B, max_new=max(new), max_len=max(total), cu_seqlens=dev(cu, torch.int32),
+                          pos0=dev(np.array(before), torch.int32), seq_len=dev(np.array(total), torch.int32))
+    q_all = dev(np.concatenate(qs).reshape(-1, H, maps * dim), torch.bfloat16)
+    kw = dict(softcap=softcap, chunk=chunk, lam=lam, norm_out=maps == 2, eps=eps, out_scale=out_scale)
+    got = ops.maps_attention(q_all, k_pool, v_pool, dev(table, torch.int32), ctx, maps, scale, impl="mma", **kw).double().cpu().numpy()
+    plain = ops.maps_attention(q_all, k_pool, v_pool, dev(table, torch.int32), ctx, maps, scale, impl="plain", **kw).double().cpu().numpy()
+    for b in range(B):
+        ref = maps_oracle(qs[b], ks[b], vs[b], before[b], maps, scale, softcap, chunk, lam, maps == 2, eps, out_scale, H, G)
+        rows = slice(cu[b], cu[b + 1])
+        rms = np.sqrt(np.mean(ref ** 2))
+        assert np.sqrt(np.mean((plain[rows] - ref) ** 2)) <= 0.006 * rms, b       # the output's own rounding to bfloat16
+        assert np.sqrt(np.mean((got[rows] - ref) ** 2)) <= 0.012 * rms, b         # and the probabilities'
+        assert np.abs(got[rows] - ref).max() <= 0.08 * np.abs(ref).max(), b
+
+
 # ----------------------------------------------------------------------------- whole models
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
