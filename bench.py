@@ -88,6 +88,25 @@ def roritar_sizes(width=2048, repeats=2, window=1024, pool=16, vocab=32768):
             "logit_scale": 1.0, "logit_softcap": 30.0}
 
 
+def punolix_sizes(width=2048, repeats=2, chunk=1024, vocab=32768):
+    """A Punolix configuration at sizes that resemble real layers: per repeat a differential attention layer (16 heads with
+    two score maps of 64 over 4 key/value heads, values of 128, scores capped at 50), a layer with two mixers side by side
+    (attention inside chunks of 1,024 positions, 16 heads of 128 over 4 key/value heads behind a convolution of 4 taps,
+    beside gated linear attention with 4 heads of 256 x 512 and a decay projection of rank 16) and another differential
+    layer, each with a gated feed-forward of 3 x width."""
+    mlp = {"kind": "dense", "ff": 3 * width}
+    diff = {"type": "attention", "mlp": mlp,
+            "mixer": {"diff": 0.8, "dim": 64, "heads": width // 128, "kv_heads": width // 512, "vdim": 128, "scale": 64 ** -0.5,
+                      "softcap": 50.0, "rot": {"base": 10000.0, "dims": 64}}}
+    left = {"conv": 4, "dim": 128, "heads": width // 128, "kv_heads": width // 512, "vdim": 128, "scale": 128 ** -0.5,
+            "mask": {"size": chunk},
+            "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"dim": width // 8, "heads": 4, "tau": 16.0, "vdim": width // 4}
+    pair = {"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Punolix", "embedding": {"scale": 1.0}, "layers": [diff, pair, diff] * repeats, "norm": {"eps": 1e-5},
+            "residual_mult": 0.7, "vocab": vocab, "width": width}
+
+
 def qwen3_beside(width=2048, layers=6, vocab=32768):
     """The closest model the library had, at the same width, depth and vocabulary: Qwen3 layers with 16 heads of 128
     (8 key/value heads) and a gated feed-forward of 3 x width."""
@@ -532,6 +551,120 @@ def roritar_kernels(torch, np, peaks) -> dict:
     return out
 
 
+def punolix_kernels(torch, np, peaks) -> dict:
+    """The Punolix design's own kernels alone at the sizes of ``punolix_sizes``, each beside the like kernel of a model the
+    library had, with the bytes or FLOPs it must move and the share of the measured peak that this comes to: attention with
+    two capped score maps and attention inside chunks, in prompts of 2,048 and 8,192 tokens and in decode steps (beside
+    Qwen3's attention: its tcgen05 and ``mma.sync`` prompt kernels and its decode kernel), the preparation of q, k and v,
+    and the gated linear recurrence (beside the gated delta rule's)."""
+    from questwend_b200.cache.manager import CacheManager
+    from questwend_b200.engine.engine import StepEntry, build_step_context
+    from questwend_b200.kernels import ops
+    from questwend_b200.parts.base import KVSpec, StateSpec
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=7):
+        times = []
+        for _ in range(reps + 3):
+            flush.zero_()                                         # L2 holds nothing of the last run
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times[3:])
+
+    def point(us, n_bytes=0, flops=0):
+        p = {"us": round(us, 1)}
+        if n_bytes:
+            p.update(gb_s=round(n_bytes / us / 1e3, 1), hbm_frac=round(n_bytes / (us * 1e-6) / hbm, 3))
+        if flops:
+            p.update(tflops=round(flops / us / 1e6, 1), tensor_frac=round(flops / (us * 1e-6) / tf, 3))
+        return p
+
+    out = {}
+    H, G, chunk, cap = 16, 4, 1024, 50.0
+    for label, n_new, B, prompt in (("prefill_2048", 2048, 1, 0), ("prefill_8192", 8192, 1, 0), ("decode_b8_at_4096", 1, 8, 4095),
+                                    ("decode_b8_at_32768", 1, 8, 32767)):
+        two, one, plain = KVSpec(G, 2 * 64, 0, value_dim=128), KVSpec(G, 128, 0, value_dim=128), KVSpec(G, 128, 0)
+        n_ctx = prompt + n_new
+        cache = CacheManager([(two, None, None), (one, None, None), (plain, None, None)], B * n_ctx + 64 * B, B, n_ctx + 64, bf, dev)
+        slots = cache.open(B)
+        if prompt:
+            build_step_context(cache, [StepEntry(s, [0] * prompt, []) for s in slots], 10, dev)
+            for s in slots:
+                cache.advance(s, prompt)
+        units = [cache.unit_cache(i) for i in range(3)]
+        for unit in units:
+            unit.k_pool.normal_()
+            unit.v_pool.normal_()
+        ctx = build_step_context(cache, [StepEntry(s, [0] * n_new, []) for s in slots], 10, dev)[0]
+        rows = B * n_new
+        u0, u1, u2 = units
+        t0, t1, t2 = (ctx.page_tables[u.group_id] for u in units)
+        q2 = torch.randn(rows, H, 2 * 64, device=dev).to(bf)
+        q1 = torch.randn(rows, H, 128, device=dev).to(bf)
+        diff = lambda: ops.maps_attention(q2, u0.k_pool, u0.v_pool, t0, ctx, 2, 0.125, softcap=cap, lam=0.6, norm_out=True, eps=1e-5, out_scale=0.2)
+        uncapped = lambda: ops.maps_attention(q2, u0.k_pool, u0.v_pool, t0, ctx, 2, 0.125, lam=0.6, norm_out=True, eps=1e-5, out_scale=0.2)
+        chunked = lambda: ops.maps_attention(q1, u1.k_pool, u1.v_pool, t1, ctx, 1, 0.09, chunk=chunk)
+        if n_new > 1:       # per (query, visible key): 2 FLOPs per key value and 2 per value, for every map
+            full = n_new * (n_new + 1) // 2
+            inside = sum(p % chunk + 1 for p in range(n_new))
+            out[f"differential_attention_{label}"] = point(timed(diff, reps=3), flops=H * full * 2 * (2 * 64 + 2 * 128))
+            out[f"differential_attention_no_cap_{label}"] = point(timed(uncapped, reps=3), flops=H * full * 2 * (2 * 64 + 2 * 128))
+            out[f"chunked_attention_{label}"] = point(timed(chunked, reps=3), flops=H * inside * 4 * 128)
+            for impl in ("tc", "mma"):
+                out[f"qwen3_attention_{impl}_{label}"] = point(timed(lambda: ops.attn_prefill(q1, u2.k_pool, u2.v_pool, t2, ctx.cu_seqlens, ctx.pos0, ctx.max_new, 0.09, impl=impl), reps=3),
+                                                               flops=H * full * 4 * 128)
+                seen = sum(min(p + 1, chunk) for p in range(n_new))
+                out[f"qwen3_attention_{impl}_window_{chunk}_{label}"] = point(timed(lambda: ops.attn_prefill(q1, u2.k_pool, u2.v_pool, t2, ctx.cu_seqlens, ctx.pos0, ctx.max_new, 0.09, window=chunk, impl=impl), reps=3),
+                                                                              flops=H * seen * 4 * 128)
+        else:               # a decode step reads the visible keys and values of every key/value head once
+            inside = (n_ctx - 1) % chunk + 1
+            out[f"differential_attention_{label}"] = point(timed(diff), B * G * n_ctx * (2 * 64 + 128) * 2)
+            out[f"chunked_attention_{label}"] = point(timed(chunked), B * G * inside * (128 + 128) * 2)
+            out[f"qwen3_attention_{label}"] = point(timed(lambda: ops.attn_decode(q1, u2.k_pool, u2.v_pool, t2, ctx.seq_len, 0.09, ctx.max_len)),
+                                                    B * G * n_ctx * 2 * 128 * 2)
+        # what stands in front of the scores: bias, norm of q and k, rotation, cache write (float in, bfloat16 out)
+        n_cols = (H + G) * 128 + G * 128
+        qkv = torch.randn(rows, n_cols, device=dev)
+        bias, nw, cs = torch.zeros(n_cols, device=dev), torch.ones(128, device=dev), torch.ones(rows, 64, device=dev)
+        out[f"maps_prep_{label}"] = point(timed(lambda: ops.maps_prep(qkv, bias, nw, nw, cs, cs, ctx, t1, u1.k_pool, u1.v_pool, H, G, 1, 128, 128, 128, False, 1e-5)),
+                                          rows * n_cols * 6)
+        del cache, units, u0, u1, u2
+        torch.cuda.empty_cache()
+    # the recurrences: one prompt of 2,048 tokens, and a step of 8 single tokens.  Gated linear attention: 4 heads of
+    # 256 x 512; the gated delta rule beside it: 16 heads of 128 x 128 (the same 0.5 M numbers of state a sequence)
+    for rows, B in ((2048, 1), (8, 8)):
+        cache = CacheManager([(None, StateSpec((4, 512, 256)), None), (None, StateSpec((16, 128, 128)), None)], 4096, 8, 4096, bf, dev)
+        slots = cache.open(B)
+        ctx = build_step_context(cache, [StepEntry(s, [0] * (rows // B), []) for s in slots], 10, dev)[0]
+        heads, K, P = 4, 256, 512
+        qkv = torch.randn(rows, heads * (2 * K + P), device=dev) * 0.1
+        a_raw, a_bias = torch.randn(rows, heads * K, device=dev), torch.zeros(heads * K, device=dev)
+        st = cache.unit_cache(0).state
+        moved = rows * heads * (3 * K + 2 * P) * 4 + (2 * B * st[0].numel() * 4 if rows == B else 0)
+        out[f"gated_linear_attention_scan_{rows}"] = point(timed(lambda: ops.gla_scan(qkv, a_raw, a_bias, st, ctx, heads, K, P, K ** -0.5, 16.0)), moved)
+        heads, K, P = 16, 128, 128
+        qkv2 = torch.randn(rows, heads * (2 * K + P), device=dev) * 0.1
+        b_raw, a_raw2 = torch.randn(rows, heads, device=dev), torch.randn(rows, heads * K, device=dev)
+        dt_bias, a_log = torch.zeros(heads * K, device=dev), torch.zeros(heads, device=dev)
+        st2 = cache.unit_cache(1).state
+        moved = rows * heads * (3 * K + 2 * P) * 4 + (2 * B * st2[0].numel() * 4 if rows == B else 0)
+        out[f"gated_delta_rule_scan_{rows}"] = point(timed(lambda: ops.delta_rule(qkv2, b_raw, 0, a_raw2, dt_bias, a_log, st2, ctx, heads, heads, K, P, 1e-6, K ** -0.5)), moved)
+        o = torch.randn(rows, 4 * 512, device=dev)
+        gate = torch.randn(rows, 4 * 512, device=dev)
+        w = torch.ones(512, device=dev)
+        out[f"gated_head_norm_{rows}"] = point(timed(lambda: ops.gated_part_norm(o, gate, 0, w, 4, 1e-5, gate_first=False, out_dtype=bf, gate_activation="silu")),
+                                               rows * 4 * 512 * 10)
+        del cache
+        torch.cuda.empty_cache()
+    return out
+
+
 def reference_arm(args) -> int:
     """kishida/questwend itself, unmodified, through its own public classes (baseline/ref_bench.cpp), on the same sizes.
     Nothing of questwend_b200 is imported on this path."""
@@ -624,9 +757,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--model", default="8b", choices=sorted(MODELS) + ["movudra", "roritar", "roritar-kernels"],
-                    help="8b: the benchmark; 0.6b, 32b: its other workloads alone; movudra, roritar: that design at real layer "
-                         "sizes beside Qwen3 layers of the same width and depth; roritar-kernels: its own kernels alone, each "
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS) + ["movudra", "roritar", "roritar-kernels", "punolix", "punolix-kernels"],
+                    help="8b: the benchmark; 0.6b, 32b: its other workloads alone; movudra, roritar, punolix: that design at real layer "
+                         "sizes beside Qwen3 layers of the same width and depth; roritar-kernels, punolix-kernels: its own kernels alone, each "
                          "beside the like kernel of a model the library had")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -666,6 +799,17 @@ def main() -> int:
         print(json.dumps({"metric": "Roritar's kernels alone, each beside the like kernel of an earlier model", "n_gpus": 1,
                           "dtype": "bf16", "data": "synthetic: random tensors of the sizes of roritar_sizes; L2 flushed between runs",
                           "peaks": peak_source, "points": roritar_kernels(torch, np, peaks)}))
+        return 0
+    if args.model == "punolix":
+        designs = (("punolix", punolix_sizes()), ("qwen3_same_size", qwen3_beside()))
+        print(json.dumps({"metric": "Punolix at real layer sizes beside Qwen3 layers of equal width and depth", "n_gpus": 1,
+                          "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
+                          "peaks": peak_source, "points": movudra_workload(torch, np, peaks, steps, warmup, designs)}))
+        return 0
+    if args.model == "punolix-kernels":
+        print(json.dumps({"metric": "Punolix's kernels alone, each beside the like kernel of an earlier model", "n_gpus": 1,
+                          "dtype": "bf16", "data": "synthetic: random tensors of the sizes of punolix_sizes; L2 flushed between runs",
+                          "peaks": peak_source, "points": punolix_kernels(torch, np, peaks)}))
         return 0
     if args.model != "8b":                      # one of the other workloads alone, as a line of its own
         points = small_model_workload(torch, np, peaks) if args.model == "0.6b" else large_model_workload(torch, np, peaks)

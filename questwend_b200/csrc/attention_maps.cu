@@ -24,7 +24,7 @@
 #define QWB_MAPS_MAX 2
 #define QWB_MAPS_ROWS 8           // (query head, map) pairs per block of the decode kernel
 #define QWB_MAPS_RUN_PAGES 2      // pages per run of the decode kernel, doubled while a sequence would have more than ...
-#define QWB_MAPS_MAX_RUNS 16      // ... this many runs: follows from the sequence's own length, not from the batch
+#define QWB_MAPS_MAX_RUNS 64      // ... this many runs: follows from the sequence's own length, not from the batch
 
 // value i of a vector after its first n values were turned by the angle whose cos and sin are cs[m], sn[m] for pair m
 __device__ __forceinline__ float maps_turned(const float* v, int i, int n, const float* cs, const float* sn, int interleaved) {
@@ -588,7 +588,7 @@ extern "C" int qwb_maps_prefill_mma(const void* q, const void* k_pool, const voi
 // ---------------------------------------------------------------------------------
 // decode: one new token per sequence (its position is len - 1).  The keys it sees, first .. len - 1 with first the start
 // of its chunk (or 0), are cut into runs of whole pages counted from the page of the first key: 2 pages a run, doubled
-// while that would give more than 16 runs.  Which keys a run holds follows from the sequence's own length alone.
+// while that would give more than 64 runs.  Which keys a run holds follows from the sequence's own length alone.
 // Block = (run, key/value head and slice of its rows, sequence), 128 threads; a row is a (query head, map) pair, up to 8 a
 // block: a page's K and V tiles go to shared memory; thread (key, half of the rows) forms the scores; a warp per row
 // updates maximum and sum; thread d accumulates p v for all rows.
@@ -666,9 +666,10 @@ __global__ void maps_decode_kernel(const T* __restrict__ q, const T* __restrict_
             uint4* kdst = reinterpret_cast<uint4*>(Kt);
             uint4* vdst = reinterpret_cast<uint4*>(Vt);
             for (int i = tid; i < n_keys * nchunk; i += blockDim.x) maps_cp16(kdst + i + i / nchunk, ksrc + i);     // row r starts at r * (nchunk + 1)
+            asm volatile("cp.async.commit_group;" ::: "memory");
             for (int i = tid; i < n_keys * vdim / VEC; i += blockDim.x) maps_cp16(vdst + i, vsrc + i);
             asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");     // the keys are there; the values arrive under the scores
         }
         __syncthreads();
 
@@ -714,6 +715,7 @@ __global__ void maps_decode_kernel(const T* __restrict__ q, const T* __restrict_
                 m_s[ri] = m_new;
             }
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
 
 #pragma unroll

@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(AT_THREADS)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ pos0, bf16* __restrict__ out, int Hq, int Hkv,
-                       int table_width, float scale, int window, int G, int* error) {
+                       int table_width, float scale, int window, int chunk, int G, int* error) {
     constexpr int ATOMS = AtSmem<HD>::ATOMS;
     constexpr uint32_t KV_BYTES = AtSmem<HD>::KV_BYTES;
     constexpr uint32_t TMEM_COLS = 256;                                     // S: 2 x 64 columns, O: HD columns
@@ -167,7 +167,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int len = p0 + n_new;
     const int last_tok = min(n_new, q0 + tok_per_block) - 1;
     const int k_last = p0 + last_tok;
-    const int k_first = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+    // with `chunk` > 0 a query sees only the keys of its own block of `chunk` positions, counted from position 0
+    const int k_first = chunk > 0 ? ((p0 + q0) / chunk) * chunk : (window > 0 ? max(0, p0 + q0 - window + 1) : 0);
     const int tile_first = k_first / AT_KEYS, tile_last = k_last / AT_KEYS;
     const int n_tiles = tile_last - tile_first + 1;
     const int* pages = page_table + (size_t)b * table_width;
@@ -300,7 +301,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             __syncwarp();
             if (lane == 0) at_arrive(&s_empty[j & 1]);
             // a tile that lies wholly inside what this row may see needs no mask
-            const bool all_visible = key0 + AT_KEYS - 1 <= qp && key0 + AT_KEYS - 1 < len && (window <= 0 || key0 > qp - window);
+            const int own = chunk > 0 && qp >= 0 ? (qp / chunk) * chunk : 0;                    // the first key of the row's own chunk
+            const bool all_visible = key0 + AT_KEYS - 1 <= qp && key0 + AT_KEYS - 1 < len && (window <= 0 || key0 > qp - window) && key0 >= own;
             float mx = -INFINITY;
             if (all_visible) {
 #pragma unroll
@@ -310,7 +312,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             } else {
                 // this row sees the tile's keys [first, end): one subtraction and one unsigned comparison per key
                 const int end = min(min(qp, len - 1) - key0 + 1, AT_KEYS);
-                const int first = window > 0 ? max(qp - window + 1 - key0, 0) : 0;
+                const int first = max(window > 0 ? max(qp - window + 1 - key0, 0) : 0, own - key0);
                 const unsigned span = end > first ? (unsigned)(end - first) : 0u;
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
@@ -420,7 +422,7 @@ static AtEncodeFn at_encode() {
 template <int HD>
 static int launch_attn_tc(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
                           const int* pos0, void* out, int B, int T, int max_new, int n_pages, int Hq, int Hkv, int table_width,
-                          float scale, int window, int* error, cudaStream_t stream) {
+                          float scale, int window, int chunk, int* error, cudaStream_t stream) {
     AtEncodeFn enc = at_encode();
     if (!enc) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: cuTensorMapEncodeTiled is not available from this driver");
     const int G = Hq / Hkv;
@@ -453,16 +455,17 @@ static int launch_attn_tc(const void* q, const void* k_pool, const void* v_pool,
     const int tok_per_block = AT_ROWS / G;
     dim3 grid(Hkv, (max_new + tok_per_block - 1) / tok_per_block, B);
     e = qwb_launch(attn_tc_prefill_kernel<HD>, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, page_table, cu_seqlens, pos0,
-                   (bf16*)out, Hq, Hkv, table_width, scale, window, G, error);
+                   (bf16*)out, Hq, Hkv, table_width, scale, window, chunk, G, error);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: launch failed: %s", cudaGetErrorString(e));
     return qwb_check_launch("attn_tc_prefill");
 }
 
 // bfloat16.  q [T, Hq, hd] with T the packed tokens of all B sequences; pools of n_pages pages; `error` as for qwb_gemm_tc.
-extern "C" int qwb_attn_tc_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
-                                   const int* cu_seqlens, const int* pos0, void* out, int B, int T, int max_new, int n_pages,
-                                   int Hq, int Hkv, int hd, int page_size, int table_width, float scale, int window, int* error,
-                                   cudaStream_t stream) {
+// `chunk` > 0: a query sees the keys of its own block of `chunk` positions only (beside the causal mask and the window).
+extern "C" int qwb_attn_tc_prefill_chunked(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                           const int* cu_seqlens, const int* pos0, void* out, int B, int T, int max_new, int n_pages,
+                                           int Hq, int Hkv, int hd, int page_size, int table_width, float scale, int window,
+                                           int chunk, int* error, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0 || T <= 0) return 0;
     if (hd != 64 && hd != 128) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: head size %d is not 64 or 128", hd);
     if (page_size != AT_KEYS) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: page size %d is not %d", page_size, AT_KEYS);
@@ -472,8 +475,17 @@ extern "C" int qwb_attn_tc_prefill(const void* q, const void* k_pool, const void
     if (B > 65535 || (max_new + AT_ROWS / G - 1) / (AT_ROWS / G) > 65535)
         return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: batch %d or %d new tokens of a sequence are more than the grid takes", B, max_new);
     if (!error) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: an error word on the device is required");
+    if (window < 0 || chunk < 0) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: window %d, chunk %d", window, chunk);
     if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16)
         return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: operands must be 16-byte aligned");
-    if (hd == 64) return launch_attn_tc<64>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, error, stream);
-    return launch_attn_tc<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, error, stream);
+    if (hd == 64) return launch_attn_tc<64>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, chunk, error, stream);
+    return launch_attn_tc<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, chunk, error, stream);
+}
+
+extern "C" int qwb_attn_tc_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                   const int* cu_seqlens, const int* pos0, void* out, int B, int T, int max_new, int n_pages,
+                                   int Hq, int Hkv, int hd, int page_size, int table_width, float scale, int window, int* error,
+                                   cudaStream_t stream) {
+    return qwb_attn_tc_prefill_chunked(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, hd,
+                                       page_size, table_width, scale, window, 0, error, stream);
 }

@@ -353,9 +353,10 @@ def tc_attention_fits(dtype: torch.dtype, head_dim: int, page_size: int, group: 
 
 
 def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, scale: float,
-                 window: int = 0, impl: str = "auto") -> torch.Tensor:
+                 window: int = 0, impl: str = "auto", chunk: int = 0) -> torch.Tensor:
     """Causal attention of new tokens over the cache.  q [T, Hq, hd]; returns [T, Hq * hd].
-    impl: "auto" (the fastest that fits), "tc" (tcgen05), "mma" (mma.sync), or "plain"."""
+    impl: "auto" (the fastest that fits), "tc" (tcgen05), "mma" (mma.sync), or "plain".  ``chunk`` > 0: a query sees only
+    the keys of its own block of ``chunk`` positions, counted from position 0 (the tcgen05 kernel only)."""
     _need(q, "q", k_pool.dtype, 3)
     _need(k_pool, "k_pool", ndim=4)
     _need(v_pool, "v_pool", k_pool.dtype, 4)
@@ -374,11 +375,13 @@ def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, 
     if use_tc:
         if q.dtype != torch.bfloat16:
             raise KernelError("attn_prefill: the tensor-core kernel takes bfloat16 only")
-        _call("attention_tc", "qwb_attn_tc_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
+        _call("attention_tc", "qwb_attn_tc_prefill_chunked", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
               _ptr(cu_seqlens), _ptr(pos0), _ptr(out), _i(B), _i(T), _i(max_new), _i(k_pool.shape[0]), _i(Hq),
-              _i(k_pool.shape[1]), _i(hd), _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window),
+              _i(k_pool.shape[1]), _i(hd), _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _i(chunk),
               _ptr(gemm_tc_error_word(q.device)), _stream())
         return out
+    if chunk:
+        raise KernelError("attn_prefill: only the tcgen05 kernel masks by chunks")
     use_mma = impl == "mma" or (impl == "auto" and mma_attention_fits(q.dtype, hd, k_pool.shape[2]))
     if use_mma:
         if q.dtype != torch.bfloat16:
@@ -1129,7 +1132,8 @@ def maps_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, maps: int, 
     then (``norm_out``) divided by its root mean square over vdim and multiplied by ``out_scale``.  Scores are scaled,
     soft-capped (``softcap`` > 0) and masked causally, and to the query's chunk of ``chunk`` positions if that is > 0.
     Steps of one token per sequence take the kernel that cuts the keys into runs (sizes that are multiples of 8); other
-    steps the tensor-core kernel where it fits (``impl`` "auto" or "mma"), else the plain one ("plain")."""
+    steps the tensor-core kernels where they fit (``impl`` "auto"; "tc": tcgen05, for one uncapped map with keys and values
+    of 64 or 128; "mma": mma.sync), else the plain one ("plain")."""
     _need(q, "q", k_pool.dtype, 3)
     T, H, kdim = q.shape
     G, vdim = k_pool.shape[1], v_pool.shape[3]
@@ -1148,6 +1152,10 @@ def maps_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, maps: int, 
               _ptr(scratch), _ptr(out), _i(_dt(q.dtype)), _i(T), _i(H), _i(G), _i(maps), _i(dim), _i(vdim), _i(width), _f(scale),
               _f(softcap), _i(chunk), _i(n_runs), _f(lam), _i(1 if norm_out else 0), _f(eps), _f(out_scale), _stream(), kernels=2)
         return out
+    # one map, no cap, keys and values of one size: the prompt kernel of plain grouped-query attention, with the chunk mask
+    if (impl in ("auto", "tc") and maps == 1 and softcap <= 0.0 and dim == vdim and q.dtype == torch.bfloat16
+            and ctx.max_new * (H // G) >= 64 and tc_attention_fits(q.dtype, dim, k_pool.shape[2], H // G)):
+        return attn_prefill(q, k_pool, v_pool, page_table, ctx.cu_seqlens, ctx.pos0, ctx.max_new, scale, impl="tc", chunk=chunk)
     if impl == "mma" or (impl == "auto" and maps_prefill_mma_fits(q.dtype, maps, dim, vdim)):
         _call("attention_maps", "qwb_maps_prefill_mma", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
               _ptr(ctx.pos0), _ptr(out), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G), _i(maps), _i(dim), _i(vdim), _i(width),

@@ -311,8 +311,11 @@ class ScoreMapsAttention(Mixer):
             self.lam = math.exp(float((lq1 * lk1).sum())) - math.exp(float((lq2 * lk2).sum())) + self.diff
 
     def kernel_modules(self):
-        return ("attention_maps", "rope_kv", "elementwise", *(("recurrent",) if self.taps else ()),
-                *linear_modules(self.runtime.dtype))
+        mods = ["attention_maps", "rope_kv", "elementwise", *(("recurrent",) if self.taps else ()), *linear_modules(self.runtime.dtype)]
+        if (self.maps == 1 and self.softcap <= 0.0 and self.head_dim == self.value_dim
+                and ops.tc_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE, self.n_heads // self.n_kv_heads)):
+            mods.append("attention_tc")         # prompts of one uncapped map with keys and values of 64 or 128
+        return tuple(mods)
 
     def kv_spec(self):
         return KVSpec(self.n_kv_heads, self.maps * self.head_dim, 0, value_dim=self.value_dim)

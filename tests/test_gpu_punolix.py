@@ -337,14 +337,17 @@ def maps_oracle(q, k, v, pos0, maps, scale, softcap, chunk, lam, norm_out, eps, 
 
 @pytest.mark.parametrize("maps, H, G, dim, vdim, chunk, softcap", [
     (2, 4, 2, 16, 32, 0, 3.0), (1, 6, 3, 32, 24, 70, 0.0), (2, 2, 1, 64, 128, 0, 0.0), (1, 2, 2, 128, 64, 64, 0.0),
-    (1, 3, 1, 48, 8, 130, 2.0), (2, 2, 2, 32, 136, 200, 5.0), (1, 1, 1, 16, 16, 1, 0.0), (2, 8, 2, 16, 40, 5, 0.0)])
+    (1, 3, 1, 48, 8, 130, 2.0), (2, 2, 2, 32, 136, 200, 5.0), (1, 1, 1, 16, 16, 1, 0.0), (2, 8, 2, 16, 40, 5, 0.0),
+    (1, 4, 2, 64, 64, 70, 0.0), (1, 8, 2, 128, 128, 200, 0.0), (1, 2, 2, 128, 128, 64, 0.0), (1, 6, 1, 64, 64, 0, 0.0),
+    (1, 3, 3, 64, 64, 1, 0.0), (1, 16, 1, 128, 128, 33, 0.0)])
 def test_tensor_core_prompt_kernel(maps, H, G, dim, vdim, chunk, softcap):
     """Sequences of unequal lengths with prompts that go on from cached tokens (positions that are not multiples of the
     tile), pages in a shuffled order; a key with a large score sits at the first position a query sees, at the one before
     it, at position 0 and at page borders.  Against float64 attention on the same bfloat16 inputs and against the plain
-    kernel."""
+    kernel.  One uncapped map with keys and values of 64 or 128 also takes the tcgen05 kernel with its chunk mask."""
     from types import SimpleNamespace
     assert ops.maps_prefill_mma_fits(torch.bfloat16, maps, dim, vdim)
+    tc = maps == 1 and softcap == 0.0 and dim == vdim and ops.tc_attention_fits(torch.bfloat16, dim, 64, H // G)
     rng = np.random.default_rng(dim + vdim + chunk)
     before, new = [0, 37, 200, 64, 5], [150, 91, 130, 1, 64]
     B, lam, eps, out_scale, scale = len(new), 0.35, 1e-5, 0.6, dim ** -0.5
@@ -377,15 +380,19 @@ def test_tensor_core_prompt_kernel(maps, H, G, dim, vdim, chunk, softcap):
                           pos0=dev(np.array(before), torch.int32), seq_len=dev(np.array(total), torch.int32))
     q_all = dev(np.concatenate(qs).reshape(-1, H, maps * dim), torch.bfloat16)
     kw = dict(softcap=softcap, chunk=chunk, lam=lam, norm_out=maps == 2, eps=eps, out_scale=out_scale)
-    got = ops.maps_attention(q_all, k_pool, v_pool, dev(table, torch.int32), ctx, maps, scale, impl="mma", **kw).double().cpu().numpy()
+    gots = [ops.maps_attention(q_all, k_pool, v_pool, dev(table, torch.int32), ctx, maps, scale, impl=impl, **kw).double().cpu().numpy()
+            for impl in (("mma", "tc") if tc else ("mma",))]
+    if tc:
+        ops.gemm_tc_check(DEV)
     plain = ops.maps_attention(q_all, k_pool, v_pool, dev(table, torch.int32), ctx, maps, scale, impl="plain", **kw).double().cpu().numpy()
     for b in range(B):
         ref = maps_oracle(qs[b], ks[b], vs[b], before[b], maps, scale, softcap, chunk, lam, maps == 2, eps, out_scale, H, G)
         rows = slice(cu[b], cu[b + 1])
         rms = np.sqrt(np.mean(ref ** 2))
         assert np.sqrt(np.mean((plain[rows] - ref) ** 2)) <= 0.006 * rms, b       # the output's own rounding to bfloat16
-        assert np.sqrt(np.mean((got[rows] - ref) ** 2)) <= 0.012 * rms, b         # and the probabilities'
-        assert np.abs(got[rows] - ref).max() <= 0.08 * np.abs(ref).max(), b
+        for got in gots:
+            assert np.sqrt(np.mean((got[rows] - ref) ** 2)) <= 0.012 * rms, b     # and the probabilities'
+            assert np.abs(got[rows] - ref).max() <= 0.08 * np.abs(ref).max(), b
 
 
 # ----------------------------------------------------------------------------- whole models
