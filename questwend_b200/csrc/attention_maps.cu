@@ -22,7 +22,7 @@
 #define QWB_MAPS_MAX_DIM 256
 #define QWB_MAPS_PAGE 64
 #define QWB_MAPS_MAX 2
-#define QWB_MAPS_ROWS 8           // (query head, map) pairs per block of the decode kernel
+#define QWB_MAPS_ROWS 8           // (query head, map) pairs per block of the decode kernel (even: see its score loop)
 #define QWB_MAPS_RUN_PAGES 2      // pages per run of the decode kernel, doubled while a sequence would have more than ...
 #define QWB_MAPS_MAX_RUNS 64      // ... this many runs: follows from the sequence's own length, not from the batch
 
@@ -331,8 +331,24 @@ __device__ __forceinline__ uint32_t mm_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-// tanh(x) = 1 - 2 / (e^(2x) + 1): exact at both ends (e^(2x) = inf or 0), a few units of the last place in between
-__device__ __forceinline__ float mm_tanh(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+__device__ __forceinline__ float mm_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float mm_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// 16-byte pieces of a [rows][cpr pieces] tile, dealt to 128 threads in order: the thread's first piece and its stride,
+// as (row, piece) pairs, so that the copy loops divide nothing
+struct MmWalk {
+    int r0, c0, dr, dc, cpr;
+    __device__ __forceinline__ MmWalk(int tid, int pieces_per_row) : r0(tid / pieces_per_row), c0(tid % pieces_per_row),
+        dr(128 / pieces_per_row), dc(128 % pieces_per_row), cpr(pieces_per_row) {}
+    __device__ __forceinline__ void next(int& r, int& c) const { r += dr; c += dc; if (c >= cpr) { c -= cpr; ++r; } }
+};
 
 template <int NV, int MAPS>     // n-tiles of 8 value columns the accumulator has room for; score maps per head
 __global__ void __launch_bounds__(128)
@@ -367,9 +383,11 @@ maps_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const int warp_lo = p0 + q0 + warp * 16, warp_hi = warp_lo + 15;
     const int warp_first = maps_first_key(warp_hi, chunk);          // the first key that every row of the warp may see
     const float log2e = 1.4426950408889634f;
-    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
-    const float mul_s = softcap > 0.f ? scale * inv_cap : scale * log2e;   // scores in units of ln 2: exp2f below
+    // Scores in units of ln 2 (ex2 below).  With a cap c: c tanh(x / c) = c - 2 c / (e^(2 x / c) + 1), exact at both ends
+    // (e^.. = inf or 0) and a few units of the last place in between: one ex2, one rcp and one fma a score.
+    const float mul_s = softcap > 0.f ? scale / softcap * 2.f * log2e : scale * log2e;
     const float cap2 = softcap * log2e;
+    const MmWalk walk_k(tid, dim / 8), walk_v(tid, vdim / 8);
 
     float res[MAPS > 1 ? NV : 1][4];                                // map 0's normed sums, until the difference is formed
 
@@ -380,27 +398,22 @@ maps_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             const int rows = min(MM_BK, k_hi + 1 - page * MM_BK);
             const bf16* ks = k_pool + ((size_t)pages[page] * G + g_kv) * MM_BK * kdim + mp * dim;
             bf16* Kd = Kbuf + stage * MM_BK * ldq;
-            for (int idx = tid; idx < MM_BK * (dim / 8); idx += blockDim.x) {
-                const int r = idx / (dim / 8), c = (idx - r * (dim / 8)) * 8;
-                mm_cp16(Kd + r * ldq + c, ks + (size_t)(r < rows ? r : 0) * kdim + c, r < rows ? 16 : 0);
-            }
+            for (int r = walk_k.r0, c = walk_k.c0; r < MM_BK; walk_k.next(r, c))
+                mm_cp16(Kd + r * ldq + c * 8, ks + (size_t)(r < rows ? r : 0) * kdim + c * 8, r < rows ? 16 : 0);
             mm_commit();
         };
         auto copy_values = [&](int it) {                            // one commit group
             const int page = first_page + it;
             const int rows = min(MM_BK, k_hi + 1 - page * MM_BK);
             const bf16* vs = v_pool + ((size_t)pages[page] * G + g_kv) * MM_BK * vdim;
-            for (int idx = tid; idx < MM_BK * (vdim / 8); idx += blockDim.x) {
-                const int r = idx / (vdim / 8), c = (idx - r * (vdim / 8)) * 8;
-                mm_cp16(Vbuf + r * ldv + c, vs + (size_t)(r < rows ? r : 0) * vdim + c, r < rows ? 16 : 0);
-            }
+            for (int r = walk_v.r0, c = walk_v.c0; r < MM_BK; walk_v.next(r, c))
+                mm_cp16(Vbuf + r * ldv + c * 8, vs + (size_t)(r < rows ? r : 0) * vdim + c * 8, r < rows ? 16 : 0);
             mm_commit();
         };
         // this map's queries (the last readers of Qs, Kbuf and Vbuf passed the barrier that closed the map before)
-        for (int idx = tid; idx < MM_BQ * (dim / 8); idx += blockDim.x) {
-            const int r = idx / (dim / 8), c = (idx - r * (dim / 8)) * 8;
+        for (int r = walk_k.r0, c = walk_k.c0; r < MM_BQ; walk_k.next(r, c)) {
             const bool in = r < nq;
-            mm_cp16(Qs + r * ldq + c, q + ((size_t)(t0 + (in ? q0 + r : 0)) * H + h) * kdim + mp * dim + c, in ? 16 : 0);
+            mm_cp16(Qs + r * ldq + c * 8, q + ((size_t)(t0 + (in ? q0 + r : 0)) * H + h) * kdim + mp * dim + c * 8, in ? 16 : 0);
         }
         // groups in the order of their commits: [Q, K0], V0, K1, V1, K2, ...
         copy_keys(0, 0);
@@ -453,7 +466,7 @@ maps_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                             ok = key <= (e < 2 ? pos_a : pos_b) && key >= (e < 2 ? lo_a : lo_b) && key <= k_hi;
                         }
                         float v = s[j][e] * mul_s;
-                        if (softcap > 0.f) v = cap2 * mm_tanh(v);
+                        if (softcap > 0.f) v = fmaf(-2.f * cap2, mm_rcp(mm_ex2(v) + 1.f), cap2);
                         s[j][e] = ok ? v : -INFINITY;
                     }
                     mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
@@ -463,12 +476,12 @@ maps_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                 mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
                 const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
                 const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
-                const float alpha0 = exp2f(m0 - base0), alpha1 = exp2f(m1 - base1);    // m = -inf gives 0
+                const float alpha0 = mm_ex2(m0 - base0), alpha1 = mm_ex2(m1 - base1);  // m = -inf gives 0
                 float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    s[j][0] = exp2f(s[j][0] - base0); s[j][1] = exp2f(s[j][1] - base0);
-                    s[j][2] = exp2f(s[j][2] - base1); s[j][3] = exp2f(s[j][3] - base1);
+                    s[j][0] = mm_ex2(s[j][0] - base0); s[j][1] = mm_ex2(s[j][1] - base0);
+                    s[j][2] = mm_ex2(s[j][2] - base1); s[j][3] = mm_ex2(s[j][3] - base1);
                     sum0 += s[j][0] + s[j][1];
                     sum1 += s[j][2] + s[j][3];
                 }
@@ -676,21 +689,29 @@ __global__ void maps_decode_kernel(const T* __restrict__ q, const T* __restrict_
         if (my_key < n_keys) {
             const Vec16<T>* krow = reinterpret_cast<const Vec16<T>*>(Kt + (size_t)my_key * kld);
             const bool ok = base + my_key >= row_first;
+            // rows my_slice, my_slice + 2, ... of the block: r0 and the stride are even, so with one or two maps they all
+            // belong to one map, and a piece of the key is read once for all of them
+            const int mp = (r0 + my_slice) % maps;
+            float s[RT / 2];
+#pragma unroll
+            for (int k = 0; k < RT / 2; ++k) s[k] = 0.f;
+            for (int ch = 0; ch < dchunk; ++ch) {
+                float kf[VEC];
+                krow[mp * dchunk + ch].get(kf);
+#pragma unroll
+                for (int k = 0; k < RT / 2; ++k) {                  // rows past rcount hold zeros
+                    const float4* qr = reinterpret_cast<const float4*>(qs + (my_slice + 2 * k) * dim + ch * VEC);
+#pragma unroll
+                    for (int e = 0; e < VEC / 4; ++e) {
+                        const float4 qv = qr[e];
+                        s[k] += qv.x * kf[4 * e] + qv.y * kf[4 * e + 1] + qv.z * kf[4 * e + 2] + qv.w * kf[4 * e + 3];
+                    }
+                }
+            }
 #pragma unroll
             for (int k = 0; k < RT / 2; ++k) {
                 const int ri = my_slice + 2 * k;
-                if (ri < rcount) {
-                    const int mp = (r0 + ri) % maps;
-                    const float* qr = qs + ri * dim;
-                    float s = 0.f;
-                    for (int ch = 0; ch < dchunk; ++ch) {
-                        float kf[VEC];
-                        krow[mp * dchunk + ch].get(kf);
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) s += qr[ch * VEC + e] * kf[e];
-                    }
-                    sc[ri * PG + my_key] = ok ? maps_cap(s, softcap, inv_cap) : -INFINITY;
-                }
+                if (ri < rcount) sc[ri * PG + my_key] = ok ? maps_cap(s[k], softcap, inv_cap) : -INFINITY;
             }
         }
         __syncthreads();
@@ -724,7 +745,18 @@ __global__ void maps_decode_kernel(const T* __restrict__ q, const T* __restrict_
             if (d < vdim) {
 #pragma unroll
                 for (int ri = 0; ri < RT; ++ri) if (ri < rcount) acc[ri][c] *= a_s[ri];
-                for (int j = 0; j < n_keys; ++j) {
+                int j = 0;
+                for (; j + 4 <= n_keys; j += 4) {                    // four keys' weights of a row in one load
+                    const float v0 = to_f32(Vt[(size_t)j * vdim + d]), v1 = to_f32(Vt[(size_t)(j + 1) * vdim + d]);
+                    const float v2 = to_f32(Vt[(size_t)(j + 2) * vdim + d]), v3 = to_f32(Vt[(size_t)(j + 3) * vdim + d]);
+#pragma unroll
+                    for (int ri = 0; ri < RT; ++ri)
+                        if (ri < rcount) {
+                            const float4 p = *reinterpret_cast<const float4*>(sc + ri * PG + j);
+                            acc[ri][c] += p.x * v0 + p.y * v1 + p.z * v2 + p.w * v3;
+                        }
+                }
+                for (; j < n_keys; ++j) {
                     const float v = to_f32(Vt[(size_t)j * vdim + d]);
 #pragma unroll
                     for (int ri = 0; ri < RT; ++ri) if (ri < rcount) acc[ri][c] += sc[ri * PG + j] * v;

@@ -222,9 +222,38 @@ def bench_pool_attention(B, tokens, ctx, Hq, Hkv, dim, vdim, window, pool, iters
             "gb_s_of_visible_rows": (B * Hkv * (seen / tokens) * (dim + vdim) * q.element_size() / us / 1e3) if tokens == 1 else None}
 
 
+def bench_maps_attention(B, tokens, ctx, Hq, Hkv, maps, dim, vdim, softcap, chunk, iters, dtype=torch.bfloat16, impl="auto") -> dict:
+    """Attention with ``maps`` score maps per head (two: differential) over the same values: ``B`` sequences that bring
+    ``tokens`` new tokens each after ``ctx`` cached ones (tokens = 1: the decode kernels; more: a prompt kernel).  Random
+    queries, keys and values."""
+    from ..cache.manager import CacheManager
+    from ..engine.engine import StepEntry, build_step_context
+    from ..parts.base import KVSpec
+    n = ctx + tokens
+    cache = CacheManager([(KVSpec(Hkv, maps * dim, 0, value_dim=vdim), None, None)], B * n + 64 * B, B, n + 64, dtype, DEV)
+    slots = cache.open(B)
+    if ctx:
+        build_step_context(cache, [StepEntry(s, [0] * ctx, []) for s in slots], 10, DEV)
+        for s in slots:
+            cache.advance(s, ctx)
+    unit = cache.unit_cache(0)
+    unit.k_pool.normal_()
+    unit.v_pool.normal_()
+    step = build_step_context(cache, [StepEntry(s, [0] * tokens, []) for s in slots], 10, DEV)[0]
+    q = torch.randn(B * tokens, Hq, maps * dim, device=DEV).to(dtype)
+    table = step.page_tables[unit.group_id]
+    us = _time(lambda i: ops.maps_attention(q, unit.k_pool, unit.v_pool, table, step, maps, dim ** -0.5, softcap=softcap, chunk=chunk,
+                                            lam=0.5, norm_out=maps == 2, eps=1e-5, out_scale=0.5, impl=impl), 1, iters, burst=3)
+    seen = sum(p + 1 - ((p // chunk) * chunk if chunk else 0) for p in range(ctx, n))
+    return {"what": "maps_attention", "batch": B, "tokens": tokens, "ctx": ctx, "heads": Hq, "kv_heads": Hkv, "maps": maps,
+            "dim": dim, "vdim": vdim, "softcap": softcap, "chunk": chunk, "impl": impl, "us": us,
+            "tflops_of_visible_keys": 2 * B * Hq * maps * (dim + vdim) * seen / us / 1e6,
+            "gb_s_of_visible_rows": (B * Hkv * (seen / tokens) * (maps * dim + vdim) * q.element_size() / us / 1e3) if tokens == 1 else None}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "rope", "decode_shapes", "sample", "pool_attn"])
+    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "rope", "decode_shapes", "sample", "pool_attn", "maps_attn"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -249,6 +278,10 @@ def main() -> int:
     ap.add_argument("--fused", action="store_true", help="decode attention with the q/k norm, rotation and cache write inside")
     ap.add_argument("--value-dim", type=int, default=0, help="pool_attn: size of a value (default: the head size)")
     ap.add_argument("--window", type=int, default=1024, help="pool_attn: the window")
+    ap.add_argument("--maps", type=int, default=2, help="maps_attn: score maps per head")
+    ap.add_argument("--softcap", type=float, default=0.0, help="maps_attn: the cap on the scores (0: none)")
+    ap.add_argument("--chunk", type=int, default=0, help="maps_attn: positions per chunk (0: plain causal)")
+    ap.add_argument("--attn-impl", default="auto", choices=["auto", "tc", "mma", "plain"], help="maps_attn: the prompt kernel")
     ap.add_argument("--pool", type=int, default=16, help="pool_attn: tokens per pooled block")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
@@ -266,6 +299,10 @@ def main() -> int:
     elif args.what == "pool_attn":
         print(json.dumps(bench_pool_attention(args.batch, args.tokens, args.ctx if args.tokens == 1 else 0, args.heads, args.kv_heads,
                                               args.head_dim, args.value_dim or args.head_dim, args.window, args.pool, args.iters, dtype)))
+    elif args.what == "maps_attn":
+        print(json.dumps(bench_maps_attention(args.batch, args.tokens, args.ctx if args.tokens == 1 else 0, args.heads, args.kv_heads,
+                                              args.maps, args.head_dim, args.value_dim or args.head_dim, args.softcap, args.chunk,
+                                              args.iters, dtype, args.attn_impl)))
     elif args.what == "sample":
         print(json.dumps(bench_sample(args.batch, args.vocab, args.temp, args.top_k, args.top_p, args.iters)))
     elif args.what == "attn_prefill":
