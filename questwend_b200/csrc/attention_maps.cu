@@ -364,7 +364,8 @@ maps_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     bf16* Kbuf = Qs + MM_BQ * ldq;                          // [2][64][ldq]
     bf16* Vbuf = Kbuf + 2 * MM_BK * ldq;                    // [64][ldv]
 
-    const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * MM_BQ;
+    // the last queries see the most keys: their blocks start first, so that the long blocks are not the launch's tail
+    const int b = blockIdx.z, h = blockIdx.y, q0 = (int)(gridDim.x - 1 - blockIdx.x) * MM_BQ;
     const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
     if (q0 >= n) return;
     const int g_kv = h / (H / G);

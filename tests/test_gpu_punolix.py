@@ -161,7 +161,10 @@ LEFTS = [ph.left(), ph.left(heads=6, kv_heads=1, dim=8, vdim=8, dims=2, conv=4, 
          ph.left(heads=3, kv_heads=3, dim=16, vdim=136, dims=0, conv=0, size=0),
          ph.left(heads=2, kv_heads=1, dim=12, vdim=20, dims=4, conv=3, size=5),
          ph.left(heads=1, kv_heads=1, dim=8, vdim=8, dims=8, conv=7, size=1),
-         ph.left(heads=4, kv_heads=2, dim=32, vdim=16, dims=16, conv=3, size=200, scaling=(4.0, 1.0, 4.0, 64))]
+         ph.left(heads=4, kv_heads=2, dim=32, vdim=16, dims=16, conv=3, size=200, scaling=(4.0, 1.0, 4.0, 64)),
+         # keys and values of one size that the tcgen05 prompt kernel takes (bfloat16), chunks that cut its tiles
+         ph.left(heads=4, kv_heads=2, dim=64, vdim=64, dims=32, conv=3, size=70, scale=0.2),
+         ph.left(heads=3, kv_heads=1, dim=128, vdim=128, dims=128, conv=0, size=33, scale=0.15)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
