@@ -784,7 +784,8 @@ __global__ void maps_decode_kernel(const T* __restrict__ q, const T* __restrict_
 }
 
 // Per (query head, sequence): each map's a = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M), M = max_r m_r, over the
-// sequence's runs in index order; then the difference of the maps, the norm and the factor.  grid (H, B), 128 threads.
+// sequence's runs in index order; then the difference of the maps, the norm and the factor.  grid (H, B), 128 threads:
+// warp m first makes map m's weights e^(m_r - M) / L once for all columns, then thread d sums its column.
 template <typename T>
 __global__ void maps_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m, const float* __restrict__ part_l,
                                   const int* __restrict__ seq_len, T* __restrict__ out, int H, int maps, int vdim, int chunk, int n_runs,
@@ -792,26 +793,39 @@ __global__ void maps_merge_kernel(const float* __restrict__ part_acc, const floa
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float red[32];
-    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    __shared__ float wts[QWB_MAPS_MAX][QWB_MAPS_MAX_RUNS];
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int len = seq_len[b];
     const int first = maps_first_key(len - 1, chunk);
     const int rp = maps_run_pages(first, len);
     const int runs = min(n_runs, ((len - 1) / QWB_MAPS_PAGE - first / QWB_MAPS_PAGE) / rp + 1);
+    if (warp < maps) {
+        const size_t row = ((size_t)b * H + h) * maps + warp;
+        float M = -INFINITY;
+        for (int r = lane; r < runs; r += 32) M = fmaxf(M, part_m[row * n_runs + r]);
+        M = warp_max(M);
+        float L = 0.f;
+        for (int r = lane; r < runs; r += 32) {
+            const float e = M == -INFINITY ? 0.f : expf(part_m[row * n_runs + r] - M);
+            wts[warp][r] = e;
+            L += part_l[row * n_runs + r] * e;
+        }
+        L = warp_sum(L);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int r = lane; r < runs; r += 32) wts[warp][r] *= inv;
+    }
+    __syncthreads();
     float res[2] = {0.f, 0.f};
     for (int mp = 0; mp < maps; ++mp) {
         const size_t row = ((size_t)b * H + h) * maps + mp;
-        float M = -INFINITY;
-        for (int r = 0; r < runs; ++r) M = fmaxf(M, part_m[row * n_runs + r]);
-        float L = 0.f;
-        for (int r = 0; r < runs; ++r) L += part_l[row * n_runs + r] * expf(part_m[row * n_runs + r] - M);
-        const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
             const int d = tid + c * 128;
             if (d >= vdim) continue;
+            const float* col = part_acc + row * n_runs * vdim + d;
             float a = 0.f;
-            for (int r = 0; r < runs; ++r) a += part_acc[(row * n_runs + r) * vdim + d] * expf(part_m[row * n_runs + r] - M);
-            a *= inv;
+#pragma unroll 8
+            for (int r = 0; r < runs; ++r) a += col[(size_t)r * vdim] * wts[mp][r];
             res[c] = mp == 0 ? a : res[c] - lambda * a;
         }
     }
