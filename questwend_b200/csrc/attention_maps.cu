@@ -554,6 +554,196 @@ maps_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     }
 }
 
+// Two maps in ONE pass over the keys (values of up to 128): a tile's key rows hold both maps side by side, as the cache
+// has them, and so do the query rows; a warp forms map 0's scores and probabilities, then map 1's, and both products
+// with the values read each value fragment once.  Twice the accumulators (128 registers at values of 128), half the
+// tiles, copies and barriers of the kernel above, and no result of the first map to keep.
+template <int NV>
+__global__ void __launch_bounds__(128)
+maps_prefill_mma_pair_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                             const int* __restrict__ page_table, const int* __restrict__ cu_seqlens, const int* __restrict__ pos0,
+                             bf16* __restrict__ out, int H, int G, int dim, int vdim, int table_width, float scale, float softcap,
+                             int chunk, float lambda, int norm_out, float eps, float out_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int kdim = 2 * dim, ldq = kdim + MM_PAD, ldv = vdim + MM_PAD;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);           // [64][ldq]
+    bf16* Kbuf = Qs + MM_BQ * ldq;                          // [2][64][ldq]
+    bf16* Vbuf = Kbuf + 2 * MM_BK * ldq;                    // [64][ldv]
+
+    const int b = blockIdx.z, h = blockIdx.y, q0 = (int)(gridDim.x - 1 - blockIdx.x) * MM_BQ;   // long blocks first
+    const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+    if (q0 >= n) return;
+    const int g_kv = h / (H / G);
+    const int p0 = pos0[b];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nq = min(MM_BQ, n - q0);
+    const int gr = lane >> 2, tq = lane & 3;
+    const int pos_a = p0 + q0 + warp * 16 + gr, pos_b = pos_a + 8;
+    const int lo_a = maps_first_key(pos_a, chunk), lo_b = maps_first_key(pos_b, chunk);
+    const int k_hi = p0 + q0 + nq - 1, k_lo = maps_first_key(p0 + q0, chunk);
+    const int nv_used = vdim / 8;
+    const int first_page = k_lo / MM_BK, n_tiles = k_hi / MM_BK - first_page + 1;
+    const int* pages = page_table + (size_t)b * table_width;
+    const int warp_lo = p0 + q0 + warp * 16, warp_hi = warp_lo + 15;
+    const int warp_first = maps_first_key(warp_hi, chunk);
+    const float log2e = 1.4426950408889634f;
+    const float mul_s = softcap > 0.f ? scale / softcap * 2.f * log2e : scale * log2e;
+    const float cap2 = softcap * log2e;
+    const MmWalk walk_k(tid, kdim / 8), walk_v(tid, vdim / 8);
+
+    auto copy_keys = [&](int it, int stage) {
+        const int page = first_page + it;
+        const int rows = min(MM_BK, k_hi + 1 - page * MM_BK);
+        const bf16* ks = k_pool + ((size_t)pages[page] * G + g_kv) * MM_BK * kdim;
+        bf16* Kd = Kbuf + stage * MM_BK * ldq;
+        for (int r = walk_k.r0, c = walk_k.c0; r < MM_BK; walk_k.next(r, c))
+            mm_cp16(Kd + r * ldq + c * 8, ks + (size_t)(r < rows ? r : 0) * kdim + c * 8, r < rows ? 16 : 0);
+        mm_commit();
+    };
+    auto copy_values = [&](int it) {
+        const int page = first_page + it;
+        const int rows = min(MM_BK, k_hi + 1 - page * MM_BK);
+        const bf16* vs = v_pool + ((size_t)pages[page] * G + g_kv) * MM_BK * vdim;
+        for (int r = walk_v.r0, c = walk_v.c0; r < MM_BK; walk_v.next(r, c))
+            mm_cp16(Vbuf + r * ldv + c * 8, vs + (size_t)(r < rows ? r : 0) * vdim + c * 8, r < rows ? 16 : 0);
+        mm_commit();
+    };
+    for (int r = walk_k.r0, c = walk_k.c0; r < MM_BQ; walk_k.next(r, c)) {
+        const bool in = r < nq;
+        mm_cp16(Qs + r * ldq + c * 8, q + ((size_t)(t0 + (in ? q0 + r : 0)) * H + h) * kdim + c * 8, in ? 16 : 0);
+    }
+    copy_keys(0, 0);
+    copy_values(0);
+
+    float o[2][NV][4];
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+        for (int j = 0; j < NV; ++j) o[mp][j][0] = o[mp][j][1] = o[mp][j][2] = o[mp][j][3] = 0.f;
+    float m0[2] = {-INFINITY, -INFINITY}, m1[2] = {-INFINITY, -INFINITY}, l0[2] = {0.f, 0.f}, l1[2] = {0.f, 0.f};
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const bf16* Ks = Kbuf + (it & 1) * MM_BK * ldq;
+        const bf16* Vs = Vbuf;
+        const bool more = it + 1 < n_tiles;
+        if (more) { copy_keys(it + 1, (it + 1) & 1); mm_wait<2>(); } else { mm_wait<1>(); }
+        __syncthreads();
+        const int key0 = (first_page + it) * MM_BK;
+        const bool none = key0 > warp_hi || key0 + MM_BK <= maps_first_key(warp_lo, chunk);
+        const bool whole = key0 + MM_BK - 1 <= warp_lo && key0 >= warp_first;
+        uint32_t pk[2][4][4];                                       // both maps' probabilities as the second product's A operands
+        if (!none) {
+#pragma unroll
+            for (int mp = 0; mp < 2; ++mp) {
+                float s[8][4];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                for (int d = mp * dim; d < (mp + 1) * dim; d += 16) {
+                    uint32_t a0, a1, a2, a3;
+                    mm_ldsm_x4(a0, a1, a2, a3, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldq + d + (lane >> 4) * 8);
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        uint32_t b0, b1, b2, b3;
+                        mm_ldsm_x4(b0, b1, b2, b3, Ks + (j * 8 + (lane & 7) + (lane >> 4) * 8) * ldq + d + ((lane >> 3) & 1) * 8);
+                        mm_mma(s[j], a0, a1, a2, a3, b0, b1);
+                        mm_mma(s[j + 1], a0, a1, a2, a3, b2, b3);
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        bool ok = true;
+                        if (!whole) {
+                            const int key = key0 + j * 8 + tq * 2 + (e & 1);
+                            ok = key <= (e < 2 ? pos_a : pos_b) && key >= (e < 2 ? lo_a : lo_b) && key <= k_hi;
+                        }
+                        float v = s[j][e] * mul_s;
+                        if (softcap > 0.f) v = fmaf(-2.f * cap2, mm_rcp(mm_ex2(v) + 1.f), cap2);
+                        s[j][e] = ok ? v : -INFINITY;
+                    }
+                    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                    mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+                }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m0[mp], mx0), mn1 = fmaxf(m1[mp], mx1);
+                const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+                const float alpha0 = mm_ex2(m0[mp] - base0), alpha1 = mm_ex2(m1[mp] - base1);
+                float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    s[j][0] = mm_ex2(s[j][0] - base0); s[j][1] = mm_ex2(s[j][1] - base0);
+                    s[j][2] = mm_ex2(s[j][2] - base1); s[j][3] = mm_ex2(s[j][3] - base1);
+                    sum0 += s[j][0] + s[j][1];
+                    sum1 += s[j][2] + s[j][3];
+                }
+                sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+                sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+                l0[mp] = l0[mp] * alpha0 + sum0; l1[mp] = l1[mp] * alpha1 + sum1;
+                m0[mp] = mn0; m1[mp] = mn1;
+#pragma unroll
+                for (int j = 0; j < NV; ++j) { o[mp][j][0] *= alpha0; o[mp][j][1] *= alpha0; o[mp][j][2] *= alpha1; o[mp][j][3] *= alpha1; }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    pk[mp][ks][0] = mm_pack(s[2 * ks][0], s[2 * ks][1]); pk[mp][ks][1] = mm_pack(s[2 * ks][2], s[2 * ks][3]);
+                    pk[mp][ks][2] = mm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]); pk[mp][ks][3] = mm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+                }
+            }
+        }
+        if (more) mm_wait<1>(); else mm_wait<0>();                  // this tile's values are there
+        __syncthreads();
+        if (!none) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                for (int j = 0; j < NV; j += 2) {
+                    if (j < nv_used) {
+                        uint32_t b0, b1, b2, b3;
+                        mm_ldsm_x4_trans(b0, b1, b2, b3, Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + j * 8 + (lane >> 4) * 8);
+#pragma unroll
+                        for (int mp = 0; mp < 2; ++mp) {
+                            mm_mma(o[mp][j], pk[mp][ks][0], pk[mp][ks][1], pk[mp][ks][2], pk[mp][ks][3], b0, b1);
+                            if (j + 1 < NV) mm_mma(o[mp][j + 1], pk[mp][ks][0], pk[mp][ks][1], pk[mp][ks][2], pk[mp][ks][3], b2, b3);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (more) copy_values(it + 1);
+    }
+
+    const float ia0 = l0[0] > 0.f ? 1.f / l0[0] : 0.f, ia1 = l1[0] > 0.f ? 1.f / l1[0] : 0.f;
+    const float ib0 = l0[1] > 0.f ? lambda / l0[1] : 0.f, ib1 = l1[1] > 0.f ? lambda / l1[1] : 0.f;
+    float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        o[0][j][0] = o[0][j][0] * ia0 - o[1][j][0] * ib0; o[0][j][1] = o[0][j][1] * ia0 - o[1][j][1] * ib0;
+        o[0][j][2] = o[0][j][2] * ia1 - o[1][j][2] * ib1; o[0][j][3] = o[0][j][3] * ia1 - o[1][j][3] * ib1;
+        if (j < nv_used) { ss0 += o[0][j][0] * o[0][j][0] + o[0][j][1] * o[0][j][1]; ss1 += o[0][j][2] * o[0][j][2] + o[0][j][3] * o[0][j][3]; }
+    }
+    float mul0 = 1.f, mul1 = 1.f;
+    if (norm_out) {
+        ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+        ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+        mul0 = rsqrtf(ss0 / (float)vdim + eps) * out_scale;
+        mul1 = rsqrtf(ss1 / (float)vdim + eps) * out_scale;
+    }
+    const int row_a = warp * 16 + gr, row_b = row_a + 8;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        if (j < nv_used) {
+            const int col = j * 8 + tq * 2;
+            if (row_a < nq) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + q0 + row_a) * H + h) * vdim + col) = mm_pack(o[0][j][0] * mul0, o[0][j][1] * mul0);
+            if (row_b < nq) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + q0 + row_b) * H + h) * vdim + col) = mm_pack(o[0][j][2] * mul1, o[0][j][3] * mul1);
+        }
+    }
+}
+
 // Q and two key buffers [64][dim + 8] and one value buffer [64][vdim + 8] of bfloat16
 static size_t mm_smem_bytes(int dim, int vdim) {
     return ((size_t)3 * MM_BK * (dim + MM_PAD) + (size_t)MM_BK * (vdim + MM_PAD)) * sizeof(bf16);
@@ -593,7 +783,21 @@ extern "C" int qwb_maps_prefill_mma(const void* q, const void* k_pool, const voi
         if (vdim <= 32) QWB_MM(4, MAPS); else if (vdim <= 64) QWB_MM(8, MAPS); else if (vdim <= 128) QWB_MM(16, MAPS);          \
         else QWB_MM(32, MAPS);                                                                                                  \
     } while (0)
-    if (maps == 1) QWB_MM_SIZES(1); else QWB_MM_SIZES(2);
+    const size_t smem_pair = mm_smem_bytes(2 * dim, vdim);
+    if (maps == 2 && vdim <= 128 && smem_pair <= 220 * 1024) {         // both maps in one pass
+#define QWB_MM_PAIR(NV)                                                                                                         \
+    do {                                                                                                                        \
+        if (smem_pair > 48 * 1024) {                                                                                            \
+            cudaError_t e = cudaFuncSetAttribute(maps_prefill_mma_pair_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pair); \
+            if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "maps_prefill_mma: %s", cudaGetErrorString(e));                 \
+        }                                                                                                                       \
+        qwb_launch(maps_prefill_mma_pair_kernel<NV>, grid, 128, smem_pair, stream, (const bf16*)q, (const bf16*)k_pool,         \
+                   (const bf16*)v_pool, page_table, cu_seqlens, pos0, (bf16*)out, H, G, dim, vdim, table_width, scale, softcap, \
+                   chunk, lambda, norm_out, eps, out_scale);                                                                    \
+    } while (0)
+        if (vdim <= 32) QWB_MM_PAIR(4); else if (vdim <= 64) QWB_MM_PAIR(8); else QWB_MM_PAIR(16);
+#undef QWB_MM_PAIR
+    } else if (maps == 1) QWB_MM_SIZES(1); else QWB_MM_SIZES(2);
 #undef QWB_MM_SIZES
 #undef QWB_MM
     return qwb_check_launch("maps_prefill_mma");
