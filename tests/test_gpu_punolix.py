@@ -516,6 +516,40 @@ def test_a_wide_model_with_many_rows(tmp_path):
     assert close(np.stack(rows), ref, torch.bfloat16)
 
 
+def test_a_model_at_tensor_core_sizes_in_portions_and_batches(tmp_path):
+    """bfloat16 with sizes that the tensor-core prompt kernels take (two maps of 32 with values of 64: both maps in one
+    pass; one map of 64 with values of 64: the tcgen05 kernel with its chunk mask): a prompt whole, in portions that cut
+    chunks and pages, and two unequal prompts in one batch against each alone, then single tokens."""
+    cfgd = ph.config([(ph.attention(heads=4, kv_heads=2, dim=32, vdim=64, dims=16, softcap=4.0), ph.dense(ff=96)),
+                      (ph.parallel(ph.left(heads=4, kv_heads=2, dim=64, vdim=64, dims=32, conv=3, size=70, scale=0.2),
+                                   ph.right(heads=2, dim=16, vdim=24)), ph.dense(ff=72)),
+                      (ph.attention(heads=2, kv_heads=1, dim=16, vdim=128, dims=16, softcap=0.0, diff=0.1), None)],
+                     width=64, vocab=96, loop=(0, 2, 2))
+    w = ph.draw_weights(cfgd, 43)
+    folder = ph.write_folder(str(tmp_path / "m"), cfgd, w)
+    rng = np.random.default_rng(5)
+    long, short = rng.integers(0, 96, 330).tolist(), rng.integers(0, 96, 90).tolist()
+    ref_long, ref_short = pp.forward(long, w, cfgd, round16=True), pp.forward(short, w, cfgd, round16=True)
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=2048, max_batch=3)
+    for cuts in ([324], [139, 141, 44], [64, 70, 190]):
+        (s,) = eng.open_sequences(1)
+        rows, at = [], 0
+        for n in cuts:
+            rows += list(all_rows(eng, s, long[at:at + n]))
+            at += n
+        for t in long[at:]:
+            rows.append(eng.step([StepEntry(s, [t], [0])]).double().cpu().numpy()[0])
+        eng.close_sequences([s])
+        assert close(np.stack(rows), ref_long, torch.bfloat16), cuts
+    a, b = eng.open_sequences(2)
+    out = eng.step([StepEntry(a, long[:324], list(range(324))), StepEntry(b, short[:84], list(range(84)))]).double().cpu().numpy()
+    rows_a, rows_b = list(out[:324]), list(out[324:])
+    for i in range(6):
+        out = eng.step([StepEntry(a, [long[324 + i]], [0]), StepEntry(b, [short[84 + i]], [0])]).double().cpu().numpy()
+        rows_a.append(out[0]), rows_b.append(out[1])
+    assert close(np.stack(rows_a), ref_long, torch.bfloat16) and close(np.stack(rows_b), ref_short, torch.bfloat16)
+
+
 @pytest.mark.parametrize("layers", [[(ph.attention(heads=2, kv_heads=2, dim=8, vdim=8, dims=8), ph.dense(ff=8))],
                                     [(ph.parallel(ph.left(heads=2, kv_heads=1, dim=8, vdim=8, dims=4, conv=2, size=6), ph.right(heads=1, dim=8, vdim=8)), None)]],
                          ids=["no_state", "one_pair"])
