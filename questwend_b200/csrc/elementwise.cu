@@ -351,13 +351,19 @@ extern "C" int qwb_add_planes(float* x, const float* planes, const unsigned char
 // interleave 0: the first F columns are the gate and the last F the up projection;
 // interleave G > 0 (F a multiple of G): for every G features, their G gates and then their G ups.
 // ---------------------------------------------------------------------------------
-// act 0: silu; 1: gelu (tanh form)
-__device__ __forceinline__ float gate_act(float g, int act) {
-    return act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.f + expf(-g));
+// act 0: silu(g) * u; 1: gelu(g) * u (tanh form); 2: both clamped first, g <- min(g, limit) and u <- clamp(u, -limit, limit),
+// then g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float gate_mul(float g, float u, int act, float limit) {
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+    }
+    return (act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.f + expf(-g))) * u;
 }
 
 template <typename TOut>
-__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int interleave, int act) {
+__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int interleave, int act, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t n = (size_t)T * F;
@@ -366,7 +372,7 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__
         const size_t gate_at = interleave > 0 ? (f / interleave) * 2 * interleave + f % interleave : f;
         const float g = gu[t * 2 * F + gate_at];
         const float u = gu[t * 2 * F + gate_at + (interleave > 0 ? interleave : F)];
-        out[i] = from_f32<TOut>(gate_act(g, act) * u);
+        out[i] = from_f32<TOut>(gate_mul(g, u, act, limit));
     }
 }
 
@@ -374,7 +380,7 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__
 // takes 8 features: 64 bytes of gates and ups in four 16-byte loads, one store of 8 values.  64 rows of 12,288 features:
 // 3.2 us against 5.5 with a value a thread.
 template <typename TOut>
-__global__ void silu_mul_eights_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int act) {
+__global__ void silu_mul_eights_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int act, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     const int groups = F >> 3;
@@ -384,14 +390,15 @@ __global__ void silu_mul_eights_kernel(const float* __restrict__ gu, TOut* __res
         const float4* src = reinterpret_cast<const float4*>(gu + (t * 2 * F + grp * 16));
         const float4 g0 = src[0], g1 = src[1], u0 = src[2], u1 = src[3];
         TOut* dst = out + t * F + grp * 8;
-        Pack4<TOut>::store(dst, gate_act(g0.x, act) * u0.x, gate_act(g0.y, act) * u0.y, gate_act(g0.z, act) * u0.z, gate_act(g0.w, act) * u0.w);
-        Pack4<TOut>::store(dst + 4, gate_act(g1.x, act) * u1.x, gate_act(g1.y, act) * u1.y, gate_act(g1.z, act) * u1.z, gate_act(g1.w, act) * u1.w);
+        Pack4<TOut>::store(dst, gate_mul(g0.x, u0.x, act, limit), gate_mul(g0.y, u0.y, act, limit), gate_mul(g0.z, u0.z, act, limit), gate_mul(g0.w, u0.w, act, limit));
+        Pack4<TOut>::store(dst + 4, gate_mul(g1.x, u1.x, act, limit), gate_mul(g1.y, u1.y, act, limit), gate_mul(g1.z, u1.z, act, limit), gate_mul(g1.w, u1.w, act, limit));
     }
 }
 
-extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, int interleave, int act, cudaStream_t stream) {
+extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, int interleave, int act, float limit, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (act != 0 && act != 1) return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown gate activation %d", act);
+    if (act < 0 || act > 2) return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown gate activation %d", act);
+    if (act == 2 && !(limit > 0.f)) return qwb_fail(QWB_ERR_ARG, "silu_mul: the clamped gate needs a positive limit, got %g", (double)limit);
     if (F <= 0) return qwb_fail(QWB_ERR_ARG, "silu_mul: bad width %d", F);
     if (interleave < 0 || (interleave > 0 && F % interleave))
         return qwb_fail(QWB_ERR_ARG, "silu_mul: %d features cannot be interleaved in groups of %d", F, interleave);
@@ -401,15 +408,15 @@ extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int 
         (out_dtype == QWB_DT_F32 || out_dtype == QWB_DT_BF16)) {
         const size_t groups = n / 8;
         const int g8 = (int)((groups + block - 1) / block < 148 * 16 ? (groups + block - 1) / block : 148 * 16);
-        if (out_dtype == QWB_DT_F32) qwb_launch(silu_mul_eights_kernel<float>, g8, block, 0, stream, gate_up, (float*)out, T, F, act);
-        else qwb_launch(silu_mul_eights_kernel<bf16>, g8, block, 0, stream, gate_up, (bf16*)out, T, F, act);
+        if (out_dtype == QWB_DT_F32) qwb_launch(silu_mul_eights_kernel<float>, g8, block, 0, stream, gate_up, (float*)out, T, F, act, limit);
+        else qwb_launch(silu_mul_eights_kernel<bf16>, g8, block, 0, stream, gate_up, (bf16*)out, T, F, act, limit);
         return qwb_check_launch("silu_mul");
     }
     const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
     if (out_dtype == QWB_DT_F32)
-        qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F, interleave, act);
+        qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F, interleave, act, limit);
     else if (out_dtype == QWB_DT_BF16)
-        qwb_launch(silu_mul_kernel<bf16>, grid, block, 0, stream, gate_up, (bf16*)out, T, F, interleave, act);
+        qwb_launch(silu_mul_kernel<bf16>, grid, block, 0, stream, gate_up, (bf16*)out, T, F, interleave, act, limit);
     else
         return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown dtype %d", out_dtype);
     return qwb_check_launch("silu_mul");
@@ -557,6 +564,103 @@ extern "C" int qwb_rmsnorm_onto(const float* y, const float* w, float* h, void* 
         qwb_launch(rmsnorm_onto_kernel<float>, T, block, smem, stream, y, w, h, (float*)cast, D, eps);
     }
     return qwb_check_launch("rmsnorm_onto");
+}
+
+// ---------------------------------------------------------------------------------
+// The norm AFTER the sum:  h[t, :] <- norm(alpha * h[t, :] + y[t, :]) * w with norm(v) = v * rsqrt(mean(v^2) + eps), in
+// 32-bit and in place, for blocks whose stream is normed after every sublayer has been added.  `cast` (optional, float or
+// bfloat16) receives the new h in the dtype of the next product's operands.  One block per row; the row of sums stays in
+// shared memory between the two passes.
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void rmsnorm_mix_kernel(const float* __restrict__ y, const float* __restrict__ w, float* h, TOut* __restrict__ cast,
+                                   int D, float eps, float alpha) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float row_cache[];
+    __shared__ float red[32];
+    const size_t at = (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = alpha * h[at + i] + y[at + i];
+        row_cache[i] = v;
+        ss += v * v;
+    }
+    const float scale = rsqrtf(block_sum(ss, red) / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = row_cache[i] * scale * w[i];
+        h[at + i] = v;
+        if (cast) cast[at + i] = from_f32<TOut>(v);
+    }
+}
+
+// The same for rows of up to 4 x ITERS x 256 values that are whole 16-byte pieces: the row stays in registers and a
+// thread's loads are issued together.
+template <typename TOut, int ITERS>
+__global__ void __launch_bounds__(256)
+rmsnorm_mix_rows_kernel(const float* __restrict__ y, const float* __restrict__ w, float* h, TOut* __restrict__ cast, int D, float eps,
+                        float alpha) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float red[32];
+    const size_t at = (size_t)blockIdx.x * D;
+    const float4* y4 = reinterpret_cast<const float4*>(y + at);
+    float4* h4 = reinterpret_cast<float4*>(h + at);
+    float4 v[ITERS], g[ITERS];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < ITERS; ++k) {
+        const int i = threadIdx.x + k * 256;
+        const bool in = i < D / 4;
+        const float4 a = in ? y4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 r = in ? h4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        g[k] = in ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[k] = make_float4(alpha * r.x + a.x, alpha * r.y + a.y, alpha * r.z + a.z, alpha * r.w + a.w);
+        ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+    const float scale = rsqrtf(block_sum(ss, red) / (float)D + eps);
+#pragma unroll
+    for (int k = 0; k < ITERS; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < D / 4) {
+            const float4 o = make_float4(v[k].x * scale * g[k].x, v[k].y * scale * g[k].y, v[k].z * scale * g[k].z, v[k].w * scale * g[k].w);
+            h4[i] = o;
+            if (cast) Pack4<TOut>::store(cast + at + 4 * (size_t)i, o.x, o.y, o.z, o.w);
+        }
+    }
+}
+
+extern "C" int qwb_rmsnorm_mix(const float* y, const float* w, float* h, void* cast, int cast_dtype, int T, int D, float eps, float alpha,
+                               cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm_mix: bad width %d", D);
+    if (cast && cast_dtype != QWB_DT_BF16 && cast_dtype != QWB_DT_F32) return qwb_fail(QWB_ERR_ARG, "rmsnorm_mix: unknown dtype %d", cast_dtype);
+    const bool to_bf16 = cast && cast_dtype == QWB_DT_BF16;
+    const bool vec = D % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)h % 16 == 0 && (!cast || (uintptr_t)cast % 16 == 0);
+    if (vec && D / 4 <= 4 * 256) {
+        if (D / 4 <= 2 * 256) {
+            if (to_bf16) qwb_launch(rmsnorm_mix_rows_kernel<bf16, 2>, T, 256, 0, stream, y, w, h, (bf16*)cast, D, eps, alpha);
+            else qwb_launch(rmsnorm_mix_rows_kernel<float, 2>, T, 256, 0, stream, y, w, h, (float*)cast, D, eps, alpha);
+        } else {
+            if (to_bf16) qwb_launch(rmsnorm_mix_rows_kernel<bf16, 4>, T, 256, 0, stream, y, w, h, (bf16*)cast, D, eps, alpha);
+            else qwb_launch(rmsnorm_mix_rows_kernel<float, 4>, T, 256, 0, stream, y, w, h, (float*)cast, D, eps, alpha);
+        }
+        return qwb_check_launch("rmsnorm_mix");
+    }
+    const size_t smem = (size_t)D * sizeof(float);
+    if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm_mix: width %d does not fit in shared memory", D);
+    const int block = D >= 1024 ? 256 : 128;
+    cudaError_t e = cudaSuccess;
+    if (to_bf16) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_mix_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm_mix: %s", cudaGetErrorString(e));
+        qwb_launch(rmsnorm_mix_kernel<bf16>, T, block, smem, stream, y, w, h, (bf16*)cast, D, eps, alpha);
+    } else {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_mix_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm_mix: %s", cudaGetErrorString(e));
+        qwb_launch(rmsnorm_mix_kernel<float>, T, block, smem, stream, y, w, h, (float*)cast, D, eps, alpha);
+    }
+    return qwb_check_launch("rmsnorm_mix");
 }
 
 // ---------------------------------------------------------------------------------

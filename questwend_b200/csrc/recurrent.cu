@@ -19,10 +19,12 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 // zero for a new sequence).  x [T, ld] is read at column c (the caller offsets the pointer), out is [T, C].
 // in_bias, if given, is added to every input x before it is convolved (a projection's bias: the tail holds inputs with
 // it, the zeros before a sequence's start stay zeros).
+// act 0: none; 1: SiLU; 2: the token's own input is added to the sum, out = x_t + conv(x)_t.  out is float or bfloat16.
 // ---------------------------------------------------------------------------------
+template <typename TOut>
 __global__ void short_conv_kernel(const float* __restrict__ x, int ld, const float* __restrict__ w, const float* __restrict__ bias,
                                   const float* __restrict__ in_bias, const float* tail, const int* __restrict__ tok_seq, const int* __restrict__ cu_seqlens,
-                                  const int* __restrict__ slots, float* __restrict__ out, int T, int C, int taps, int act) {
+                                  const int* __restrict__ slots, TOut* __restrict__ out, int T, int C, int taps, int act) {
     pdl_wait();
     pdl_launch_dependents();
     const int c = blockIdx.y * blockDim.x + threadIdx.x, t = blockIdx.x;
@@ -32,12 +34,13 @@ __global__ void short_conv_kernel(const float* __restrict__ x, int ld, const flo
     float acc = bias ? bias[c] : 0.f;
     const float ib = in_bias ? in_bias[c] : 0.f;
     const float* tl = tail + (size_t)slots[b] * (taps - 1) * C;
+    float v = 0.f;
     for (int j = 0; j < taps; ++j) {
         const int src = i - (taps - 1 - j);
-        const float v = src >= 0 ? x[(size_t)(t - (taps - 1 - j)) * ld + c] + ib : tl[(size_t)(taps - 1 + src) * C + c];
+        v = src >= 0 ? x[(size_t)(t - (taps - 1 - j)) * ld + c] + ib : tl[(size_t)(taps - 1 + src) * C + c];
         acc += w[c * taps + j] * v;
     }
-    out[(size_t)t * C + c] = act ? silu_f(acc) : acc;
+    out[(size_t)t * C + c] = from_f32<TOut>(act == 1 ? silu_f(acc) : (act == 2 ? acc + v : acc));
 }
 
 // The tail after the step: the last taps - 1 inputs of each sequence (new ones, then what is left of the old tail).
@@ -59,8 +62,9 @@ __global__ void conv_tail_kernel(const float* __restrict__ x, int ld, const floa
 }
 
 // A step of one token per sequence: the convolution and the new tail by one thread per (sequence, channel).
+template <typename TOut>
 __global__ void short_conv_step_kernel(const float* __restrict__ x, int ld, const float* __restrict__ w, const float* __restrict__ bias,
-                                       const float* __restrict__ in_bias, float* tail, const int* __restrict__ slots, float* __restrict__ out, int B, int C, int taps,
+                                       const float* __restrict__ in_bias, float* tail, const int* __restrict__ slots, TOut* __restrict__ out, int B, int C, int taps,
                                        int act, int update_tail) {
     pdl_wait();
     pdl_launch_dependents();
@@ -74,32 +78,43 @@ __global__ void short_conv_step_kernel(const float* __restrict__ x, int ld, cons
         keep[r] = tl[(size_t)r * C + c];
         acc += w[c * taps + r] * keep[r];
     }
-    out[(size_t)b * C + c] = act ? silu_f(acc) : acc;
+    out[(size_t)b * C + c] = from_f32<TOut>(act == 1 ? silu_f(acc) : (act == 2 ? acc + cur : acc));
     if (update_tail) {
         for (int r = 0; r + 1 < taps - 1; ++r) tl[(size_t)r * C + c] = keep[r + 1];
         if (taps > 1) tl[(size_t)(taps - 2) * C + c] = cur;
     }
 }
 
-extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const float* bias, const float* in_bias, float* tail, const int* tok_seq,
-                              const int* cu_seqlens, const int* slots, float* out, int T, int B, int C, int taps, int act,
-                              int update_tail, int single_token, cudaStream_t stream) {
-    if (T <= 0 || B <= 0) return 0;
-    if (C <= 0 || taps < 1 || taps > QWB_CONV_MAX_TAPS || ld < C)
-        return qwb_fail(QWB_ERR_ARG, "short_conv: %d channels, %d taps (1 to %d), row stride %d", C, taps, QWB_CONV_MAX_TAPS, ld);
-    if (B > 65535 || C > 65535 * 128) return qwb_fail(QWB_ERR_ARG, "short_conv: %d sequences or %d channels are too many", B, C);
+template <typename TOut>
+static int launch_short_conv(const float* x, int ld, const float* w, const float* bias, const float* in_bias, float* tail, const int* tok_seq,
+                             const int* cu_seqlens, const int* slots, TOut* out, int T, int B, int C, int taps, int act,
+                             int update_tail, int single_token, cudaStream_t stream) {
     const int block = C >= 256 ? 256 : 128;
     if (single_token && T == B) {
-        qwb_launch(short_conv_step_kernel, dim3(B, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, in_bias, tail, slots, out, B, C, taps, act, update_tail);
+        qwb_launch(short_conv_step_kernel<TOut>, dim3(B, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, in_bias, tail, slots, out, B, C, taps, act, update_tail);
         return qwb_check_launch("short_conv_step");
     }
-    qwb_launch(short_conv_kernel, dim3(T, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, in_bias, (const float*)tail, tok_seq, cu_seqlens, slots, out, T, C, taps, act);
+    qwb_launch(short_conv_kernel<TOut>, dim3(T, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, in_bias, (const float*)tail, tok_seq, cu_seqlens, slots, out, T, C, taps, act);
     if (int rc = qwb_check_launch("short_conv")) return rc;
     if (update_tail && taps > 1) {
         qwb_launch(conv_tail_kernel, dim3((C + block - 1) / block, B), block, 0, stream, x, ld, in_bias, tail, cu_seqlens, slots, B, C, taps);
         return qwb_check_launch("conv_tail");
     }
     return 0;
+}
+
+extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const float* bias, const float* in_bias, float* tail, const int* tok_seq,
+                              const int* cu_seqlens, const int* slots, void* out, int out_dtype, int T, int B, int C, int taps, int act,
+                              int update_tail, int single_token, cudaStream_t stream) {
+    if (T <= 0 || B <= 0) return 0;
+    if (C <= 0 || taps < 1 || taps > QWB_CONV_MAX_TAPS || ld < C || act < 0 || act > 2)
+        return qwb_fail(QWB_ERR_ARG, "short_conv: %d channels, %d taps (1 to %d), row stride %d, mode %d", C, taps, QWB_CONV_MAX_TAPS, ld, act);
+    if (B > 65535 || C > 65535 * 128) return qwb_fail(QWB_ERR_ARG, "short_conv: %d sequences or %d channels are too many", B, C);
+    if (out_dtype == QWB_DT_F32)
+        return launch_short_conv<float>(x, ld, w, bias, in_bias, tail, tok_seq, cu_seqlens, slots, (float*)out, T, B, C, taps, act, update_tail, single_token, stream);
+    if (out_dtype == QWB_DT_BF16)
+        return launch_short_conv<bf16>(x, ld, w, bias, in_bias, tail, tok_seq, cu_seqlens, slots, (bf16*)out, T, B, C, taps, act, update_tail, single_token, stream);
+    return qwb_fail(QWB_ERR_ARG, "short_conv: unknown dtype %d", out_dtype);
 }
 
 // ---------------------------------------------------------------------------------
@@ -308,11 +323,12 @@ extern "C" int qwb_ssm_scan(const float* xbc, int ldx, const float* dt_raw, int 
 // Preparation, one block per token: q and k (after convolution and SiLU) become unit vectors per head,
 // x / sqrt(sum x^2 + unit_eps), q times q_scale; kq = k . q; beta = sigmoid(b_raw); decay[h, n] =
 // exp(-exp(A_log[h]) softplus(a_raw[h, n] + dt_bias[h, n])).  b_raw: H columns of a matrix with rows of ld_b values.
+// decay_k = K: a decay per head and key channel; decay_k = 1: one per head (a_raw then has H columns, in rows of ld_a).
 //   qkv [T, ld]: q [Hk * K] | k [Hk * K] | v [H * P], q and k normalised in place
 // ---------------------------------------------------------------------------------
 __global__ void delta_prep_kernel(float* qkv, int ld, float* __restrict__ kq, const float* __restrict__ b_raw, int ld_b, float* __restrict__ beta,
-                                  const float* __restrict__ a_raw, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
-                                  float* __restrict__ decay, int H, int Hk, int K, float unit_eps, float q_scale) {
+                                  const float* __restrict__ a_raw, int ld_a, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                  float* __restrict__ decay, int H, int Hk, int K, int decay_k, float unit_eps, float q_scale) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -335,16 +351,17 @@ __global__ void delta_prep_kernel(float* qkv, int ld, float* __restrict__ kq, co
         if (lane == 0) kq[(size_t)t * Hk + kh] = dot;
     }
     for (int i = threadIdx.x; i < H; i += blockDim.x) beta[(size_t)t * H + i] = sigmoid_f(b_raw[(size_t)t * ld_b + i]);
-    for (int i = threadIdx.x; i < H * K; i += blockDim.x)
-        decay[(size_t)t * H * K + i] = expf(-expf(A_log[i / K]) * softplus_f(a_raw[(size_t)t * H * K + i] + dt_bias[i]));
+    for (int i = threadIdx.x; i < H * decay_k; i += blockDim.x)
+        decay[(size_t)t * H * decay_k + i] = expf(-expf(A_log[i / decay_k]) * softplus_f(a_raw[(size_t)t * ld_a + i] + dt_bias[i]));
 }
 
-extern "C" int qwb_delta_prep(float* qkv, int ld, float* kq, const float* b_raw, int ld_b, float* beta, const float* a_raw,
-                              const float* dt_bias, const float* A_log, float* decay, int T, int H, int Hk, int K,
+extern "C" int qwb_delta_prep(float* qkv, int ld, float* kq, const float* b_raw, int ld_b, float* beta, const float* a_raw, int ld_a,
+                              const float* dt_bias, const float* A_log, float* decay, int T, int H, int Hk, int K, int decay_k,
                               float unit_eps, float q_scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || Hk <= 0 || K <= 0 || H % Hk) return qwb_fail(QWB_ERR_ARG, "delta_prep: %d heads, %d key heads of %d", H, Hk, K);
-    qwb_launch(delta_prep_kernel, T, 128, 0, stream, qkv, ld, kq, b_raw, ld_b, beta, a_raw, dt_bias, A_log, decay, H, Hk, K, unit_eps, q_scale);
+    if ((decay_k != K && decay_k != 1) || ld_a < H * decay_k) return qwb_fail(QWB_ERR_ARG, "delta_prep: %d decays a head (1 or %d) in rows of %d", decay_k, K, ld_a);
+    qwb_launch(delta_prep_kernel, T, 128, 0, stream, qkv, ld, kq, b_raw, ld_b, beta, a_raw, ld_a, dt_bias, A_log, decay, H, Hk, K, decay_k, unit_eps, q_scale);
     return qwb_check_launch("delta_prep");
 }
 
@@ -382,22 +399,71 @@ extern "C" int qwb_gla_prep(float* qkv, int ld, float* kq, const float* a_raw, c
     return qwb_check_launch("gla_prep");
 }
 
+// Preparation for linear attention with positions, one block per token: the first rdims values of every head of q and k
+// are turned (value i with value i + rdims / 2) by the token's angles (cos_t, sin_t [T, rdims / 2]; rdims 0: no turn), then
+// q times q_scale and k times k_scale in place, and kq = k . q per head.  qkv [T, ld]: q [H * K] | k [H * K] | v.
+__global__ void turn_qk_prep_kernel(float* qkv, int ld, float* __restrict__ kq, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                    int H, int K, int rdims, float q_scale, float k_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const int half = rdims >> 1;
+    float* row = qkv + (size_t)t * ld;
+    const float* cs = cos_t + (size_t)t * half;
+    const float* sn = sin_t + (size_t)t * half;
+    for (int h = warp; h < H; h += nwarp) {
+        float* q = row + h * K;
+        float* k = row + (H + h) * K;
+        float dot = 0.f;
+        for (int i = lane; i < half; i += 32) {
+            const float c = cs[i], s = sn[i];
+            const float qa = q[i], qb = q[i + half], ka = k[i], kb = k[i + half];
+            const float q0 = (qa * c - qb * s) * q_scale, q1 = (qb * c + qa * s) * q_scale;
+            const float k0 = (ka * c - kb * s) * k_scale, k1 = (kb * c + ka * s) * k_scale;
+            q[i] = q0; q[i + half] = q1; k[i] = k0; k[i + half] = k1;
+            dot += q0 * k0 + q1 * k1;
+        }
+        for (int i = rdims + lane; i < K; i += 32) {
+            const float qv = q[i] * q_scale, kv = k[i] * k_scale;
+            q[i] = qv; k[i] = kv;
+            dot += qv * kv;
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) kq[(size_t)t * H + h] = dot;
+    }
+}
+
+extern "C" int qwb_turn_qk_prep(float* qkv, int ld, float* kq, const float* cos_t, const float* sin_t, int T, int H, int K, int rdims,
+                                float q_scale, float k_scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || K <= 0 || rdims < 0 || rdims > K || rdims % 2 || ld < 2 * H * K)
+        return qwb_fail(QWB_ERR_ARG, "turn_qk_prep: %d heads of %d, %d turned, rows of %d", H, K, rdims, ld);
+    if (rdims > 0 && (!cos_t || !sin_t)) return qwb_fail(QWB_ERR_ARG, "turn_qk_prep: a rotation without its table");
+    qwb_launch(turn_qk_prep_kernel, T, 128, 0, stream, qkv, ld, kq, cos_t, sin_t, H, K, rdims, q_scale, k_scale);
+    return qwb_check_launch("turn_qk_prep");
+}
+
 // The recurrence, per head h (key head kh = h / (H / Hk)), per token, S is K x P:
 //     S = decay[:, None] * S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q
 // o is formed as (decayed S)^T q + u (k . q), so that both sums over the rows are taken in one pass.  A warp per
 // column, as above; state [slots, H, P, K].  Without `beta` (null) the write is the plain outer product, u = v: gated
-// linear attention, S = decay[:, None] * S + k v^T.
+// linear attention, S = decay[:, None] * S + k v^T.  The decays of token t, head h: decay_k = K values at decay +
+// t * decay_ts + h * K (one per key channel), or decay_k = 1 value at decay + t * decay_ts + h (one per head; with
+// decay_ts = 0 the same H numbers for every token: a fixed decay per head).
 template <int PER, bool VEC, int TB, int CW>
 __global__ void __launch_bounds__(32 * QWB_SCAN_WARPS)
 delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ kq, const float* __restrict__ beta,
                   const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ cu_seqlens,
-                  const int* __restrict__ slots, float* __restrict__ o, int H, int Hk, int K, int P, int write_state) {
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int Hk, int K, int P, int write_state,
+                  int decay_ts, int decay_k) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int p0 = (blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5)) * CW, h = blockIdx.y, b = blockIdx.z;
     if (p0 >= P) return;                                            // P is a multiple of CW: a warp's columns all exist
     const int kh = h / (H / Hk);
+    const bool per_channel = decay_k > 1 || K == 1;
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     const int n0 = lane * PER;
     float* S = state + (((size_t)slots[b] * H + h) * P + p0) * K;
@@ -416,7 +482,12 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
             const float* row = qkv + (size_t)t * ld;
             load_rows<PER, VEC>(row + kh * K, n0, K, qn[j]);
             load_rows<PER, VEC>(row + (Hk + kh) * K, n0, K, kn[j]);
-            load_rows<PER, VEC>(decay + ((size_t)t * H + h) * K, n0, K, gn[j]);
+            if (per_channel) load_rows<PER, VEC>(decay + (size_t)t * decay_ts + h * K, n0, K, gn[j]);
+            else {
+                const float one = decay[(size_t)t * decay_ts + h];
+#pragma unroll
+                for (int k = 0; k < PER; ++k) gn[j][k] = one;
+            }
 #pragma unroll
             for (int c = 0; c < CW; ++c) v_n[j][c] = row[v_at + c];
             bt_n[j] = beta ? beta[(size_t)t * H + h] : 0.f; kq_n[j] = kq[(size_t)t * Hk + kh];
@@ -441,7 +512,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
                 const float* row = qkv + (size_t)t * ld;
                 prefetch_l2(row + kh * K + n0);
                 prefetch_l2(row + (Hk + kh) * K + n0);
-                prefetch_l2(decay + ((size_t)t * H + h) * K + n0);
+                if (per_channel) prefetch_l2(decay + (size_t)t * decay_ts + h * K + n0);
                 if (lane == 0) prefetch_l2(row + v_at);
             }
         }
@@ -482,17 +553,20 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
 
 extern "C" int qwb_delta_scan(const float* qkv, int ld, const float* kq, const float* beta, const float* decay, float* state,
                               const int* cu_seqlens, const int* slots, float* o, int B, int H, int Hk, int K, int P,
-                              int write_state, cudaStream_t stream) {
+                              int write_state, int decay_ts, int decay_k, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (H <= 0 || Hk <= 0 || K <= 0 || P <= 0 || H % Hk) return qwb_fail(QWB_ERR_ARG, "delta_scan: %d heads, %d key heads, state %d x %d", H, Hk, K, P);
+    if ((decay_k != K && decay_k != 1) || decay_ts < 0 || (decay_ts != 0 && decay_ts < H * decay_k))
+        return qwb_fail(QWB_ERR_ARG, "delta_scan: %d decays a head (1 or %d), %d a token", decay_k, K, decay_ts);
     const int per = scan_rows_per_lane(K);
     if (!per) return qwb_fail(QWB_ERR_ARG, "delta_scan: a state of %d rows per head is too large (up to %d)", K, 32 * QWB_SCAN_MAX_PER);
     if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "delta_scan: %d sequences or %d heads are too many", B, H);
-    const bool vec = per >= 4 && K % 4 == 0 && ld % 4 == 0 && aligned16(qkv) && aligned16(decay) && aligned16(state);
+    const bool vec = per >= 4 && K % 4 == 0 && ld % 4 == 0 && aligned16(qkv) && aligned16(state) &&
+                     (decay_k != K || (aligned16(decay) && decay_ts % 4 == 0));
     int cw = per <= 4 && P % 4 == 0 ? 4 : (per <= 8 && P % 2 == 0 ? 2 : 1);            // columns a warp, as in ssm_scan
     if (cw > QWB_DELTA_CW_MAX) cw = QWB_DELTA_CW_MAX;
     const dim3 grid((P / cw + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
-#define QWB_DELTA1(PER, VEC, CW) qwb_launch(delta_scan_kernel<PER, VEC, (PER <= 4 ? 4 : (PER == 8 ? 2 : 1)), CW>, grid, 32 * QWB_SCAN_WARPS, 0, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state)
+#define QWB_DELTA1(PER, VEC, CW) qwb_launch(delta_scan_kernel<PER, VEC, (PER <= 4 ? 4 : (PER == 8 ? 2 : 1)), CW>, grid, 32 * QWB_SCAN_WARPS, 0, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state, decay_ts, decay_k)
 #define QWB_DELTA(PER, VEC) do { if (cw == 4 && PER <= 4) QWB_DELTA1(PER, VEC, (PER <= 4 ? 4 : 1)); else if (cw >= 2 && PER <= 8) QWB_DELTA1(PER, VEC, (PER <= 8 ? 2 : 1)); else QWB_DELTA1(PER, VEC, 1); } while (0)
     if (per == 1) QWB_DELTA(1, false); else if (per == 2) QWB_DELTA(2, false);
     else if (per == 4) { if (vec) QWB_DELTA(4, true); else QWB_DELTA(4, false); }

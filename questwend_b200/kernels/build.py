@@ -26,7 +26,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 EXTRA_FLAGS: dict[str, list[str]] = {}
 NVCC_FLAGS += os.environ.get("QWB200_NVCC_FLAGS", "").split()      # more flags (-D switches) for experiments; part of the stamp
 MODULES = ("elementwise", "layernorm", "rope_kv", "attention", "attention_mma", "attention_tc", "attention_latent", "attention_latent_mma",
-           "attention_pool", "attention_maps", "recurrent", "rglru", "moe",
+           "attention_pool", "attention_maps", "attention_bias", "recurrent", "rglru", "moe",
            "gemm_small", "gemm_stream", "gemm_ring", "gemm_tc", "sampling")
 
 _lock = threading.Lock()

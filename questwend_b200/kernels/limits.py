@@ -71,3 +71,14 @@ def maps_attention_refusal(maps: int, dim: int, vdim: int) -> str | None:
         if n <= 0 or n > MAPS_ATTN_MAX_DIM:
             return f"the attention with score maps takes {what} sizes up to {MAPS_ATTN_MAX_DIM}, not {n}"
     return None
+
+
+SHAPED_ATTN_MAX_DIM = 256   # the attention with shaped scores takes key and value sizes up to this (csrc/attention_bias.cu:
+                            # QWB_BIAS_MAX_DIM); sizes that are multiples of 8 take the kernels that copy 16 bytes at a time
+
+
+def shaped_attention_refusal(dim: int, vdim: int) -> str | None:
+    for what, n in (("key", dim), ("value", vdim)):
+        if n <= 0 or n > SHAPED_ATTN_MAX_DIM:
+            return f"the attention with shaped scores takes {what} sizes up to {SHAPED_ATTN_MAX_DIM}, not {n}"
+    return None

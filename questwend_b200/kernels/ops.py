@@ -162,12 +162,14 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GATE_U
     return torch.cat([gate.reshape(F // group, group, K), up.reshape(F // group, group, K)], dim=1).reshape(2 * F, K).contiguous()
 
 
-GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}      # what a gated feed-forward may put on its gate
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}      # what a gated feed-forward may put on its gate
 
 
-def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0, activation: str = "silu") -> torch.Tensor:
+def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0, activation: str = "silu",
+             limit: float = 0.0) -> torch.Tensor:
     """act(gate) * up from a float32 [T, 2F] matrix: gate columns first (``interleave`` 0), or for every
-    ``interleave`` features their gates and then their ups.  ``activation``: one of ``GATE_ACTIVATIONS``."""
+    ``interleave`` features their gates and then their ups.  ``activation``: one of ``GATE_ACTIVATIONS``;
+    "clamped_swish" is g sigmoid(1.702 g) (u + 1) with g = min(gate, ``limit``) and u = up clamped to +-``limit``."""
     if activation not in GATE_ACTIVATIONS:
         raise KernelError(f"silu_mul: unknown gate activation '{activation}'")
     _need(gate_up, "gate_up", torch.float32, 2)
@@ -176,7 +178,7 @@ def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0,
         raise KernelError(f"silu_mul: {F2} columns cannot be split into gate and up")
     out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
     _call("elementwise", "qwb_silu_mul", _ptr(gate_up), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(F2 // 2), _i(interleave),
-          _i(GATE_ACTIVATIONS[activation]), _stream())
+          _i(GATE_ACTIVATIONS[activation]), _f(limit), _stream())
     return out
 
 
@@ -205,6 +207,27 @@ def rmsnorm_onto(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: fl
         cast = torch.empty((T, D), dtype=cast_dtype, device=h.device)
     _call("elementwise", "qwb_rmsnorm_onto", _ptr(y), _ptr(weight), _ptr(h), _ptr(cast),
           _i(_dt(cast_dtype) if cast is not None else DT_F32), _i(T), _i(D), _f(eps), _stream())
+    if cast_dtype is None:
+        return None
+    return h if cast is None else cast
+
+
+def rmsnorm_mix(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, alpha: float = 1.0,
+                cast_dtype: torch.dtype | None = None):
+    """The norm after the sum, in place on the float32 stream ``h`` [T, D]: h <- v * rsqrt(mean(v^2) + eps) * weight with
+    v = alpha * h + y (``y`` float32 [T, D], a sublayer's output).  With ``cast_dtype`` also returns the new h in that
+    dtype (h itself for float32), else None."""
+    _need(h, "h", torch.float32, 2)
+    _need(y, "y", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    T, D = h.shape
+    if y.shape != h.shape or weight.numel() != D:
+        raise KernelError(f"rmsnorm_mix: y {tuple(y.shape)}, weight of {weight.numel()} for a stream {tuple(h.shape)}")
+    cast = None
+    if cast_dtype is not None and cast_dtype != torch.float32:
+        cast = torch.empty((T, D), dtype=cast_dtype, device=h.device)
+    _call("elementwise", "qwb_rmsnorm_mix", _ptr(y), _ptr(weight), _ptr(h), _ptr(cast),
+          _i(_dt(cast.dtype) if cast is not None else DT_F32), _i(T), _i(D), _f(eps), _f(alpha), _stream())
     if cast_dtype is None:
         return None
     return h if cast is None else cast
@@ -787,16 +810,20 @@ CONV_MAX_TAPS = 16
 
 def short_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None,
                tail: torch.Tensor, ctx, activation: bool = True, update_tail: bool = True,
-               in_bias: torch.Tensor | None = None) -> torch.Tensor:
+               in_bias: torch.Tensor | None = None, plus_input: bool = False,
+               out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """Causal convolution over time, per channel, of columns ``col0 .. col0 + channels`` of float32 ``x`` [T, ld], with
-    SiLU after it (``activation``).  ``weight`` [channels, taps]: the last tap is the current token's.  ``tail``
+    SiLU after it (``activation``), or (``plus_input``, no activation) with the token's own input added to it:
+    x + conv(x).  ``weight`` [channels, taps]: the last tap is the current token's.  ``tail``
     [slots, taps - 1, channels] float32 holds each sequence's last inputs (zero for a new one) and is brought up to
     date (``update_tail``).  ``in_bias`` [channels] is added to every input before the convolution (the bias of the
     projection that made x; the tail holds inputs with it).  ``ctx``: the step (tok_seq, cu_seqlens, slots).
-    Returns float32 [T, channels]."""
+    Returns [T, channels] in ``out_dtype`` (float32 or bfloat16)."""
     _need(x, "x", torch.float32, 2)
     _need(weight, "weight", torch.float32, 2)
     _need(tail, "tail", torch.float32, 3)
+    if plus_input and activation:
+        raise KernelError("short_conv: the input is added to a convolution without an activation")
     T, ld = x.shape
     taps = weight.shape[1]
     if weight.shape[0] != channels or col0 < 0 or col0 + channels > ld:
@@ -808,10 +835,11 @@ def short_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, 
             _need(t, name, torch.float32, 1)
             if t.numel() != channels:
                 raise KernelError(f"short_conv: {name} of {t.numel()} for {channels} channels")
-    out = torch.empty((T, channels), dtype=torch.float32, device=x.device)
+    out = torch.empty((T, channels), dtype=out_dtype, device=x.device)
     _call("recurrent", "qwb_short_conv", ctypes.c_void_p(x.data_ptr() + 4 * col0), _i(ld), _ptr(weight), _ptr(bias),
-          _ptr(in_bias), _ptr(tail), _ptr(ctx.tok_seq), _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(out), _i(T), _i(ctx.n_seqs),
-          _i(channels), _i(taps), _i(1 if activation else 0), _i(1 if update_tail else 0),
+          _ptr(in_bias), _ptr(tail), _ptr(ctx.tok_seq), _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(out), _i(_dt(out_dtype)),
+          _i(T), _i(ctx.n_seqs), _i(channels), _i(taps), _i(2 if plus_input else (1 if activation else 0)),
+          _i(1 if update_tail else 0),
           _i(1 if ctx.single_token else 0), _stream(),
           kernels=2 if (update_tail and taps > 1 and not ctx.single_token) else 1)
     return out
@@ -842,11 +870,13 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_col0: int, dt_bias, a_log, 
 
 def delta_rule(qkv: torch.Tensor, b_raw: torch.Tensor, b_col0: int, a_raw: torch.Tensor, dt_bias, a_log,
                state: torch.Tensor, ctx, heads: int, key_heads: int, key_dim: int, vdim: int, unit_eps: float,
-               q_scale: float, write_state: bool = True) -> torch.Tensor:
+               q_scale: float, write_state: bool = True, per_head: bool = False, a_col0: int = 0) -> torch.Tensor:
     """The gated delta rule with a decay per head and key channel, over a step's tokens.  ``qkv`` float32
     [T, 2 * key_heads * key_dim + heads * vdim] (q | k | v after convolution and SiLU; q and k are made unit vectors
     in place, q times ``q_scale``); columns ``b_col0 .. b_col0 + heads`` of ``b_raw`` [T, ld] and ``a_raw``
-    [T, heads * key_dim] are the raw write strengths and decays; ``state`` float32 [slots, heads, vdim, key_dim] (column by column).  Returns o float32 [T, heads * vdim]."""
+    [T, heads * key_dim] are the raw write strengths and decays; ``state`` float32 [slots, heads, vdim, key_dim] (column by column).  Returns o float32 [T, heads * vdim].
+    ``per_head``: one decay per head instead: the raw decays are columns ``a_col0 .. a_col0 + heads`` of ``a_raw`` [T, ld],
+    ``dt_bias`` has ``heads`` entries."""
     _need(qkv, "qkv", torch.float32, 2)
     _need(b_raw, "b_raw", torch.float32, 2)
     _need(a_raw, "a_raw", torch.float32, 2)
@@ -854,23 +884,60 @@ def delta_rule(qkv: torch.Tensor, b_raw: torch.Tensor, b_col0: int, a_raw: torch
     _need(dt_bias, "dt_bias", torch.float32, 1)
     _need(a_log, "A_log", torch.float32, 1)
     T = qkv.shape[0]
+    decay_k = 1 if per_head else key_dim
     if (qkv.shape[1] != 2 * key_heads * key_dim + heads * vdim or b_raw.shape[0] != T or b_col0 + heads > b_raw.shape[1]
-            or tuple(a_raw.shape) != (T, heads * key_dim) or tuple(state.shape[1:]) != (heads, vdim, key_dim)
-            or dt_bias.numel() != heads * key_dim or a_log.numel() != heads):
+            or a_raw.shape[0] != T or a_col0 < 0 or a_col0 + heads * decay_k > a_raw.shape[1]
+            or (not per_head and a_raw.shape[1] != heads * key_dim) or tuple(state.shape[1:]) != (heads, vdim, key_dim)
+            or dt_bias.numel() != heads * decay_k or a_log.numel() != heads):
         raise KernelError(f"delta_rule: qkv {tuple(qkv.shape)}, b {tuple(b_raw.shape)}, a {tuple(a_raw.shape)}, state "
                           f"{tuple(state.shape)} do not fit {heads} heads ({key_heads} key heads) of {key_dim} x {vdim}")
     dev = qkv.device
     kq = torch.empty((T, key_heads), dtype=torch.float32, device=dev)
     beta = torch.empty((T, heads), dtype=torch.float32, device=dev)
-    decay = torch.empty((T, heads * key_dim), dtype=torch.float32, device=dev)
+    decay = torch.empty((T, heads * decay_k), dtype=torch.float32, device=dev)
     _call("recurrent", "qwb_delta_prep", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), ctypes.c_void_p(b_raw.data_ptr() + 4 * b_col0),
-          _i(b_raw.shape[1]), _ptr(beta), _ptr(a_raw),
-          _ptr(dt_bias), _ptr(a_log), _ptr(decay), _i(T), _i(heads), _i(key_heads), _i(key_dim), _f(unit_eps), _f(q_scale),
-          _stream())
+          _i(b_raw.shape[1]), _ptr(beta), ctypes.c_void_p(a_raw.data_ptr() + 4 * a_col0), _i(a_raw.shape[1]),
+          _ptr(dt_bias), _ptr(a_log), _ptr(decay), _i(T), _i(heads), _i(key_heads), _i(key_dim), _i(decay_k), _f(unit_eps),
+          _f(q_scale), _stream())
     o = torch.empty((T, heads * vdim), dtype=torch.float32, device=dev)
     _call("recurrent", "qwb_delta_scan", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(beta), _ptr(decay), _ptr(state),
           _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(o), _i(ctx.n_seqs), _i(heads), _i(key_heads), _i(key_dim), _i(vdim),
-          _i(1 if write_state else 0), _stream())
+          _i(1 if write_state else 0), _i(heads * decay_k), _i(decay_k), _stream())
+    return o
+
+
+def retention_scan(qkv: torch.Tensor, cos, sin, rotary_dim: int, decay: torch.Tensor, state: torch.Tensor, ctx, heads: int,
+                   key_dim: int, vdim: int, q_scale: float, k_scale: float, write_state: bool = True) -> torch.Tensor:
+    """Linear attention with a fixed decay per head over a step's tokens: per head S = decay_h S + k v^T, o = S^T q.
+    ``qkv`` float32 [T, ld] whose first 2 * heads * key_dim + heads * vdim columns are q | k | v; the first
+    ``rotary_dim`` values of every head of q and k are turned by the tokens' angles (``cos``, ``sin`` float32
+    [T, rotary_dim / 2]; value i with value i + rotary_dim / 2), then q is multiplied by ``q_scale`` and k by ``k_scale``,
+    in place.  ``decay`` float32 [heads]; ``state`` float32 [slots, heads, vdim, key_dim] (column by column) is read and
+    written back.  Returns o float32 [T, heads * vdim].  The recurrence is the delta rule's kernel without its correction
+    term."""
+    _need(qkv, "qkv", torch.float32, 2)
+    _need(state, "state", torch.float32, 4)
+    _need(decay, "decay", torch.float32, 1)
+    T = qkv.shape[0]
+    if (qkv.shape[1] < heads * (2 * key_dim + vdim) or decay.numel() != heads
+            or tuple(state.shape[1:]) != (heads, vdim, key_dim)):
+        raise KernelError(f"retention_scan: qkv {tuple(qkv.shape)}, {decay.numel()} decays, state {tuple(state.shape)} do not "
+                          f"fit {heads} heads of {key_dim} x {vdim}")
+    if cos is None:
+        rotary_dim = 0
+    for name, t in (("cos", cos), ("sin", sin)):
+        if t is not None:
+            _need(t, name, torch.float32, 2)
+            if tuple(t.shape) != (T, rotary_dim // 2):
+                raise KernelError(f"retention_scan: table {name} {tuple(t.shape)} for {T} tokens and {rotary_dim} turned values")
+    dev = qkv.device
+    kq = torch.empty((T, heads), dtype=torch.float32, device=dev)
+    _call("recurrent", "qwb_turn_qk_prep", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(cos), _ptr(sin), _i(T), _i(heads),
+          _i(key_dim), _i(rotary_dim), _f(q_scale), _f(k_scale), _stream())
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=dev)
+    _call("recurrent", "qwb_delta_scan", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(None), _ptr(decay), _ptr(state),
+          _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(o), _i(ctx.n_seqs), _i(heads), _i(heads), _i(key_dim), _i(vdim),
+          _i(1 if write_state else 0), _i(0), _i(1), _stream())
     return o
 
 
@@ -902,7 +969,7 @@ def gla_scan(qkv: torch.Tensor, a_raw: torch.Tensor, a_bias: torch.Tensor | None
     o = torch.empty((T, heads * vdim), dtype=torch.float32, device=dev)
     _call("recurrent", "qwb_delta_scan", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(None), _ptr(decay), _ptr(state),
           _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(o), _i(ctx.n_seqs), _i(heads), _i(heads), _i(key_dim), _i(vdim),
-          _i(1 if write_state else 0), _stream())
+          _i(1 if write_state else 0), _i(heads * key_dim), _i(key_dim), _stream())
     return o
 
 
@@ -1164,6 +1231,105 @@ def maps_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, maps: int, 
     _call("attention_maps", "qwb_maps_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
           _ptr(ctx.pos0), _ptr(out), _i(_dt(q.dtype)), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G), _i(maps), _i(dim), _i(vdim),
           _i(width), _f(scale), _f(softcap), _i(chunk), _f(lam), _i(1 if norm_out else 0), _f(eps), _f(out_scale), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- attention with shaped scores
+BIAS_ATTN_MAX_DIM = 256     # csrc/attention_bias.cu: QWB_BIAS_MAX_DIM
+BIAS_ATTN_FAST_STEP = 8     # key and value sizes that are multiples of this take the kernels that copy 16 bytes at a time
+
+
+def bias_prep(qkv: torch.Tensor, bias, q_weight, k_weight, cos, sin, ctx, page_table, k_pool, v_pool, n_heads: int,
+              n_kv_heads: int, dim: int, vdim: int, rotary_dim: int, interleaved: bool, eps: float, store_kv: bool = True,
+              values_are_keys: bool = False) -> torch.Tensor:
+    """Bias (float32 over all columns, or None), per-head RMS norm of q and k (weights [dim] shared by the heads, or None),
+    rotation of the first ``rotary_dim`` values of every head of q and k, cache write.  ``qkv`` float32 [T, ld]: its
+    first (H + G) * dim + G * vdim columns, or (H + G) * dim with ``values_are_keys``: the cached value of a token is then
+    the raw output of its key projection (with the bias): what the key was ahead of its norm and its turn.  The pools [pages, G, 64, dim] / [pages, G, 64, vdim].
+    Returns q [T, H, dim] in the cache's dtype."""
+    _need(qkv, "qkv", torch.float32, 2)
+    T = qkv.shape[0]
+    ld = (n_heads + n_kv_heads) * dim + (0 if values_are_keys else n_kv_heads * vdim)
+    if qkv.shape[1] < ld:
+        raise KernelError(f"bias_prep: qkv {tuple(qkv.shape)} for {n_heads}+{n_kv_heads} heads of {dim}, values of {vdim}")
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE_SIZE, dim) or tuple(v_pool.shape[1:]) != (n_kv_heads, PAGE_SIZE, vdim):
+        raise KernelError(f"bias_prep: pools {tuple(k_pool.shape)}, {tuple(v_pool.shape)} do not fit")
+    for name, t, n in (("bias", bias, ld), ("q_weight", q_weight, dim), ("k_weight", k_weight, dim)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != n:
+                raise KernelError(f"bias_prep: {name} of {t.numel()}, wanted {n}")
+    if cos is None:
+        rotary_dim = 0
+    for name, t in (("cos", cos), ("sin", sin)):
+        if t is not None:
+            _need(t, name, torch.float32, 2)
+            if tuple(t.shape) != (T, rotary_dim // 2):
+                raise KernelError(f"bias_prep: table {name} {tuple(t.shape)} for {T} tokens and {rotary_dim} turned values")
+    q = torch.empty((T, n_heads, dim), dtype=k_pool.dtype, device=qkv.device)
+    _call("attention_bias", "qwb_bias_prep", _ptr(qkv), _ptr(bias), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
+          _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(page_table), _i(page_table.shape[1]), _ptr(q), _ptr(k_pool), _ptr(v_pool),
+          _i(_dt(k_pool.dtype)), _i(T), _i(n_heads), _i(n_kv_heads), _i(dim), _i(vdim), _i(rotary_dim),
+          _i(1 if interleaved else 0), _f(eps), _i(1 if store_kv else 0), _i(1 if values_are_keys else 0), _i(qkv.shape[1]), _stream())
+    return q
+
+
+def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: float, head_scale=None, softcap: float = 0.0,
+                   slopes=None, window: int = 0, sinks=None, head_mix=None, gate=None, gate_col0: int = 0) -> torch.Tensor:
+    """Softmax attention of a step's tokens with scores shaped head by head.  ``q`` [T, H, dim] in the cache's dtype;
+    returns [T, H * vdim] in that dtype.  score = q . k * ``scale`` * ``head_scale``[h]; capped (``softcap`` > 0:
+    c tanh(s / c)); minus ``slopes``[h] times the key's distance from the query; causal, and within the last ``window``
+    positions if that is > 0; ``sinks``[h]: one more term exp(sink) in the softmax's denominator.  ``head_mix`` [H, H]:
+    the heads' weights are mixed after the softmax, w'_h = sum_g mix[h, g] w_g, each head still reading its own value
+    head.  ``gate``: head h's output times sigmoid of column ``gate_col0 + h`` of the float32 matrix ``gate`` [T, ld].
+    The per-head vectors are float32 [H].  Steps of one token per sequence take the kernel that cuts the keys into runs
+    (sizes that are multiples of 8), other steps the plain prompt kernel."""
+    _need(q, "q", k_pool.dtype, 3)
+    T, H, dim = q.shape
+    G, vdim = k_pool.shape[1], v_pool.shape[3]
+    if k_pool.shape[3] != dim or v_pool.shape[1] != G:
+        raise KernelError(f"bias_attention: q {tuple(q.shape)}, keys {tuple(k_pool.shape)}, values {tuple(v_pool.shape)}")
+    for name, t in (("head_scale", head_scale), ("slopes", slopes), ("sinks", sinks)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != H:
+                raise KernelError(f"bias_attention: {name} of {t.numel()} for {H} heads")
+    if head_mix is not None:
+        _need(head_mix, "head_mix", torch.float32, 2)
+        if tuple(head_mix.shape) != (H, H):
+            raise KernelError(f"bias_attention: a mix {tuple(head_mix.shape)} for {H} heads")
+    if gate is not None:
+        _need(gate, "gate", torch.float32, 2)
+        if gate.shape[0] != T or gate_col0 < 0 or gate_col0 + H > gate.shape[1]:
+            raise KernelError(f"bias_attention: gate {tuple(gate.shape)} from column {gate_col0} for {T} tokens of {H} heads")
+    all_values = head_mix is not None
+    raw = all_values or gate is not None
+    C = G if all_values else 1
+    width = page_table.shape[1]
+    dev = q.device
+    att = torch.empty((T, H, C, vdim) if raw else (T, H * vdim), dtype=torch.float32 if raw else q.dtype, device=dev)
+    if ctx.single_token and dim % BIAS_ATTN_FAST_STEP == 0 and vdim % BIAS_ATTN_FAST_STEP == 0:
+        lib = _lookup("attention_bias", "qwb_bias_decode_runs")[0]
+        n_runs = lib.qwb_bias_decode_runs(_i(ctx.max_len), _i(window))
+        lib.qwb_bias_decode_scratch_floats.restype = ctypes.c_longlong
+        scratch = torch.empty((lib.qwb_bias_decode_scratch_floats(_i(T), _i(H), _i(C), _i(vdim), _i(n_runs)),),
+                              dtype=torch.float32, device=dev)
+        _call("attention_bias", "qwb_bias_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.seq_len),
+              _ptr(scratch), _ptr(att), _i(_dt(q.dtype)), _i(1 if raw else 0), _i(T), _i(H), _i(G), _i(1 if all_values else 0),
+              _i(dim), _i(vdim), _i(width), _f(scale), _ptr(head_scale), _f(softcap), _ptr(slopes), _i(window), _ptr(sinks),
+              _i(n_runs), _stream(), kernels=2)
+    else:
+        _call("attention_bias", "qwb_bias_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
+              _ptr(ctx.pos0), _ptr(att), _i(_dt(q.dtype)), _i(1 if raw else 0), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G),
+              _i(1 if all_values else 0), _i(dim), _i(vdim), _i(width), _f(scale), _ptr(head_scale), _f(softcap), _ptr(slopes),
+              _i(window), _ptr(sinks), _stream())
+    if not raw:
+        return att
+    out = torch.empty((T, H * vdim), dtype=q.dtype, device=dev)
+    _call("attention_bias", "qwb_bias_head_mix", _ptr(att), _ptr(head_mix),
+          ctypes.c_void_p(gate.data_ptr() + 4 * gate_col0) if gate is not None else _ptr(None),
+          _i(gate.shape[1] if gate is not None else 0), _ptr(out), _i(_dt(q.dtype)), _i(T), _i(H), _i(G),
+          _i(1 if all_values else 0), _i(vdim), _stream())
     return out
 
 

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them."""
-from . import qwen3, movudra, roritar, punolix  # noqa: F401
+from . import qwen3, movudra, roritar, punolix, sagupel  # noqa: F401

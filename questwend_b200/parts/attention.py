@@ -9,7 +9,8 @@ import math
 import torch
 
 from ..kernels import ops
-from ..kernels.limits import conv_taps_refusal, head_dim_refusal, maps_attention_refusal, pool_attention_refusal
+from ..kernels.limits import (conv_taps_refusal, head_dim_refusal, maps_attention_refusal, pool_attention_refusal,
+                              shaped_attention_refusal)
 from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
 from .base import KVSpec, Mixer, StateSpec, take_weight
 from .linear import kernel_modules as linear_modules, linear, linear_onto
@@ -346,6 +347,133 @@ class ScoreMapsAttention(Mixer):
         return ops.bias_act(out, self.b_o, "none", torch.float32) if self.b_o is not None else out
 
 
+class ShapedScoreAttention(Mixer):
+    """Grouped-query softmax attention whose scores are shaped head by head, each step optional and a parameter.  In
+    front of the scores: biases on q and k (and v), an RMS norm of every head of q and k with a weight shared by the
+    heads, a rotation of the first part of every head.  ``values_from_keys``: there is no value projection; a token's
+    value is the raw output of its key projection (with its bias), ahead of the key's norm and turn.  score = q . k * ``scale``, times a learned
+    number per head (``head_temperature``), capped (``softcap``: c tanh(s / c)), minus slope_h * (i - j) with
+    slope_h = 2^(-``slope_base`` (h + 1) / H) (``slope_base`` > 0); causal, and within the last ``window`` positions if
+    that is > 0; ``sink``: a learned number per head whose exponential joins the softmax's denominator (no key, no value).
+    ``head_mix``: a learned [H, H] matrix mixes the heads' weights after the softmax, w'_h = sum_g M[h, g] w_g, each head
+    still reading its own value head.  ``head_gate``: head h's output times sigmoid(W_g h)_h, one number per head.
+
+    params: hidden_size, n_heads, n_kv_heads, head_dim, value_dim, biases, values_from_keys, qk_norm, norm_eps, scale
+    (default 1/sqrt(head_dim)), head_temperature, softcap (0: none), slope_base (0: none), window (0: all keys), sink,
+    head_mix, head_gate, layout ("halves": pairs (i, i + n/2); "interleaved": (2i, 2i + 1)), names (optional overrides).
+    ``position``: an encoding that gives cos and sin [T, n/2], or None.  The cache: keys and values per token."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "q_norm": "q.norm",
+             "k_norm": "k.norm", "temp": "temp", "sink": "sink", "mix": "talk", "gate": "g"}
+    LAYOUTS = ("halves", "interleaved")
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads, self.n_kv_heads = int(p["n_heads"]), int(p["n_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.value_dim = int(p.get("value_dim", self.head_dim))
+        self.biases = bool(p.get("biases", False))
+        self.values_from_keys = bool(p.get("values_from_keys", False))
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("norm_eps", 0.0))
+        self.scale = float(p.get("scale", 1.0 / math.sqrt(self.head_dim)))
+        self.head_temperature = bool(p.get("head_temperature", False))
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        self.slope_base = float(p.get("slope_base", 0.0) or 0.0)
+        self.window = int(p.get("window", 0) or 0)
+        self.sink, self.head_mix, self.head_gate = (bool(p.get(k, False)) for k in ("sink", "head_mix", "head_gate"))
+        self.layout = str(p.get("layout", "halves"))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        self.position = position[0] if isinstance(position, (tuple, list)) else position
+        self.rotary_dim = getattr(self.position, "rotary_dim", 0) if self.position is not None else 0
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} key/value heads")
+        if self.layout not in self.LAYOUTS:
+            raise ValueError(f"attention '{self.prefix}': layout '{self.layout}' is not one of {', '.join(self.LAYOUTS)}")
+        refusal = shaped_attention_refusal(self.head_dim, self.value_dim)
+        if refusal:
+            raise ValueError(f"attention '{self.prefix}': {refusal}")
+        if self.values_from_keys and self.value_dim != self.head_dim:
+            raise ValueError(f"attention '{self.prefix}': values that are the keys have the keys' size {self.head_dim}, "
+                             f"not {self.value_dim}")
+        if self.rotary_dim > self.head_dim:
+            raise ValueError(f"rotary size {self.rotary_dim} exceeds the head size {self.head_dim}")
+        self.n_q = self.n_heads * self.head_dim
+        self.n_k = self.n_kv_heads * self.head_dim
+        self.n_v = 0 if self.values_from_keys else self.n_kv_heads * self.value_dim
+        self.temp = self.sinks = self.mix = self.slopes = None
+
+    def _projections(self):
+        return "qk" if self.values_from_keys else "qkv"
+
+    def tensors(self):
+        n, px, D, H = self.names, self.prefix, self.hidden, self.n_heads
+        sizes = {"q": self.n_q, "k": self.n_k, "v": self.n_v}
+        out = [TensorSpec(px + n[x], (sizes[x], D), MATRIX) for x in self._projections()]
+        out.append(TensorSpec(px + n["o"], (D, H * self.value_dim), MATRIX))
+        if self.biases:
+            out += [TensorSpec(px + n[x + "_bias"], (sizes[x],), VECTOR) for x in self._projections()]
+        if self.qk_norm:
+            out += [TensorSpec(px + n["q_norm"], (self.head_dim,), VECTOR, NORM_WEIGHT),
+                    TensorSpec(px + n["k_norm"], (self.head_dim,), VECTOR, NORM_WEIGHT)]
+        if self.head_temperature:
+            out.append(TensorSpec(px + n["temp"], (H,), VECTOR, NORM_WEIGHT))
+        if self.sink:
+            out.append(TensorSpec(px + n["sink"], (H,), VECTOR))
+        if self.head_mix:
+            out.append(TensorSpec(px + n["mix"], (H, H), VECTOR))
+        if self.head_gate:
+            out.append(TensorSpec(px + n["gate"], (H, D), MATRIX))
+        return out
+
+    def bind(self, weights):
+        n, px, H = self.names, self.prefix, self.n_heads
+
+        def f32(name):
+            return weights[px + n[name]].to(torch.float32).contiguous()
+
+        # one projection for everything that reads the mixer's input: q | k | (v) | (gate)
+        mats = [take_weight(weights, px + n[x]) for x in self._projections()]
+        if self.head_gate:
+            mats.append(take_weight(weights, px + n["gate"]))
+        self.w_in = torch.cat(mats, dim=0).contiguous()
+        self.w_o = weights[px + n["o"]]
+        self.b_in = torch.cat([f32(x + "_bias") for x in self._projections()]).contiguous() if self.biases else None
+        self.q_norm_w = f32("q_norm") if self.qk_norm else None
+        self.k_norm_w = f32("k_norm") if self.qk_norm else None
+        self.temp = f32("temp") if self.head_temperature else None
+        self.sinks = f32("sink") if self.sink else None
+        self.mix = f32("mix") if self.head_mix else None
+        if self.slope_base > 0:
+            slopes = [2.0 ** (-self.slope_base * (h + 1) / H) for h in range(H)]
+            self.slopes = torch.tensor(slopes, dtype=torch.float32, device=self.w_o.device)
+
+    def kernel_modules(self):
+        return ("attention_bias", "rope_kv", *linear_modules(self.runtime.dtype))
+
+    def kv_spec(self):
+        return KVSpec(self.n_kv_heads, self.head_dim, self.window, value_dim=self.value_dim)
+
+    def forward(self, x, ctx, cache):
+        proj = linear(x, self.w_in)
+        cos = sin = None
+        if self.position is not None and self.rotary_dim:
+            cos, sin = self.position.prepare(ctx)
+        table = ctx.page_tables[cache.group_id]
+        q = ops.bias_prep(proj, self.b_in, self.q_norm_w, self.k_norm_w, cos, sin, ctx, table, cache.k_pool, cache.v_pool,
+                          self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim, self.rotary_dim,
+                          self.layout == "interleaved", self.eps, store_kv=cache.writable,
+                          values_are_keys=self.values_from_keys)
+        att = ops.bias_attention(q, cache.k_pool, cache.v_pool, table, ctx, self.scale, head_scale=self.temp,
+                                 softcap=self.softcap, slopes=self.slopes, window=self.window, sinks=self.sinks,
+                                 head_mix=self.mix, gate=proj if self.head_gate else None,
+                                 gate_col0=self.n_q + self.n_k + self.n_v)
+        return linear(att, self.w_o)
+
+
 register_mixer("gqa", GroupedQueryAttention)
+register_mixer("shaped_score_attention", ShapedScoreAttention)
 register_mixer("window_pool_attention", WindowPoolAttention)
 register_mixer("score_maps_attention", ScoreMapsAttention)

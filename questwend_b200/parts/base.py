@@ -214,6 +214,8 @@ class Mixer(Part):
 
     adds_to_residual = False    # True: forward(..., residual=h) adds its output onto h in place and returns None, or
                                 # returns what is still to be added (a tensor, or a SplitSum that the next norm adds)
+    reads_stream = False        # True: a block whose sublayers read the stream itself hands forward() the 32-bit stream
+                                # instead of its copy in the engine's dtype (the mixer works on it in 32-bit first)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: UnitCache) -> torch.Tensor:
         raise NotImplementedError

@@ -200,7 +200,70 @@ class ParallelResidualBlock(Block):
         return h, ScaledSum(y, self.mult)
 
 
+class PostNormBlock(Block):
+    """h <- norm1(alpha * h + mixer(h)); h <- norm2(alpha * h + feed_forward(h)): the sublayers read the stream itself,
+    and the stream is normed AFTER each sum, so that what a layer hands on is a normed row.  The stream, both sums and
+    the norms are 32-bit; the norm kernel forms the sum, norms it, writes it back and also hands out the row in the
+    dtype of the next product's operands.  A mixer that says ``reads_stream`` gets the 32-bit stream.  A layer without a
+    feed-forward (``feed_forward`` None) has the first half only.
+    params: mixer_norm, ffn_norm (the norms' tensor names after the layer's prefix), mixer_prefix, ffn_prefix, alpha
+    (the constant on the stream in both sums; default 1)."""
+
+    def __init__(self, spec, runtime, layer=None, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        px = spec.prefix
+        self.alpha = float(p.get("alpha", 1.0))
+
+        def norm(name):
+            return build_part("norm", replace(layer.norm, prefix=px, params={**dict(layer.norm.params), "name": name}), runtime)
+
+        self.norm1 = norm(p.get("mixer_norm", "norm1"))
+        if not hasattr(self.norm1, "norm_sum"):
+            raise ValueError(f"block '{px}': the norm '{layer.norm.kind}' cannot norm a sum in place")
+        self.mixer = build_part("mixer", replace(layer.mixer, prefix=px + p.get("mixer_prefix", "mix") + "."),
+                                runtime, position=position)
+        self.ffn = self.norm2 = None
+        if layer.feed_forward is not None:
+            self.norm2 = norm(p.get("ffn_norm", "norm2"))
+            self.ffn = build_part("feed_forward", replace(layer.feed_forward, prefix=px + p.get("ffn_prefix", "mlp") + "."), runtime)
+
+    def parts(self):
+        return [part for part in (self.norm1, self.mixer, self.norm2, self.ffn) if part is not None]
+
+    def tensors(self):
+        return [t for part in self.parts() for t in part.tensors()]
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+
+    def kernel_modules(self):
+        return ("elementwise", *(m for part in self.parts() for m in part.kernel_modules()))
+
+    def forward(self, h, delta, ctx, cache):
+        from ..kernels import ops
+        dtype = self.runtime.dtype
+        if delta is not None:                                   # a block of another arrangement came before
+            if hasattr(delta, "add_onto"):
+                delta.add_onto(h)
+            else:
+                ops.add_inplace(h, delta)
+        if self.mixer.reads_stream:
+            x = h
+        else:
+            have = ctx.shared.get("stream_as_operand")
+            x = have[1] if have is not None and have[0] is h else ops.bias_act(h, None, "none", dtype)
+        # the stream in the products' dtype is made where a feed-forward follows; the next block makes its own if it needs one
+        x = self.norm1.norm_sum(h, self.mixer.forward(x, ctx, cache), self.alpha, cast_dtype=dtype if self.ffn is not None else None)
+        ctx.shared.pop("stream_as_operand", None)
+        if self.ffn is not None:
+            self.norm2.norm_sum(h, self.ffn.forward(x, ctx), self.alpha)
+        return h, None
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("post_norm", PostNormBlock)
 register_block("sandwich_norm", SandwichNormBlock)
 register_block("output_norm", OutputNormBlock)
 register_block("parallel_residual", ParallelResidualBlock)

@@ -5,14 +5,15 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..weights.manifest import MATRIX, VECTOR, TensorSpec
+from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
 from .base import Part, StreamStep
 from .linear import kernel_modules as linear_modules, linear
 from .registry import register_embedding, register_head, register_stream_step
 
 
 class TokenEmbedding(Part):
-    """params: vocab_size, hidden_size, name, scale (the rows are multiplied by it; default 1)."""
+    """params: vocab_size, hidden_size, name, scale (the rows are multiplied by it; default 1), norm (the tensor name of
+    an RMS norm's weight that the rows pass right after the gather; default none) with norm_eps."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -20,19 +21,27 @@ class TokenEmbedding(Part):
         self.hidden = int(spec.params["hidden_size"])
         self.name = self.prefix + spec.params.get("name", "embed_tokens.weight")
         self.scale = float(spec.params.get("scale", 1.0))
-        self.table = None
+        self.norm = None if spec.params.get("norm") is None else self.prefix + str(spec.params["norm"])
+        self.norm_eps = float(spec.params.get("norm_eps", 0.0))
+        self.table = self.norm_w = None
 
     def tensors(self):
-        return [TensorSpec(self.name, (self.vocab, self.hidden), MATRIX)]
+        out = [TensorSpec(self.name, (self.vocab, self.hidden), MATRIX)]
+        if self.norm is not None:
+            out.append(TensorSpec(self.norm, (self.hidden,), VECTOR, NORM_WEIGHT))
+        return out
 
     def bind(self, weights):
         self.table = weights[self.name]
+        if self.norm is not None:
+            self.norm_w = weights[self.norm].to(torch.float32).contiguous()
 
     def kernel_modules(self):
         return ("elementwise",)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return ops.embed_gather(token_ids, self.table, scale=self.scale)
+        h = ops.embed_gather(token_ids, self.table, scale=self.scale)
+        return h if self.norm_w is None else ops.rmsnorm(h, self.norm_w, self.norm_eps, torch.float32)
 
 
 class EmbeddingReinjection(StreamStep):

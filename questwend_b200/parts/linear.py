@@ -144,9 +144,9 @@ def settle(h: torch.Tensor, delta, norm=None):
 
 
 def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0,
-                  activation: str = "silu") -> torch.Tensor:
+                  activation: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """act(x Wg^T) * (x Wu^T) for the stacked weight [2F, K] -> [M, F] in ``out_dtype``; ``activation`` is one of
-    ``ops.GATE_ACTIVATIONS`` (the products with a fused epilogue have the SiLU only).  ``interleave`` 0: gate rows
+    ``ops.GATE_ACTIVATIONS`` (the products with a fused epilogue have the SiLU only; ``limit`` is the clamped form's bound).  ``interleave`` 0: gate rows
     first; ``ops.GATE_UP_GROUP``: gate and up rows interleaved in groups of that many features, which lets the products
     with a fused epilogue find a feature's gate and up in one thread."""
     if activation == "silu" and interleave == ops.GATE_UP_GROUP and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
@@ -155,7 +155,7 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torc
                 return _stream(x, weight_gate_up, None, "swiglu")
         if x.shape[0] >= TC_SWIGLU_MIN_ROWS and x.shape[1] >= TC_SWIGLU_MIN_INNER and x.shape[1] % 8 == 0:
             return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
-    return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave, activation)
+    return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave, activation, limit)
 
 
 def linear_act(x: torch.Tensor, weight: torch.Tensor, bias, activation: str, out_dtype: torch.dtype, params=None) -> torch.Tensor:

@@ -1,4 +1,6 @@
-"""Dense gated feed-forward: down( silu(gate(x)) * up(x) ) (the reference: core/runtime.cpp:1074-1076)."""
+"""Dense gated feed-forward: down( silu(gate(x)) * up(x) ) (the reference: core/runtime.cpp:1074-1076), with other gates
+as parameters: the tanh form of GELU, and a clamped form, g sigmoid(1.702 g) (u + 1) with g = min(gate(x), limit) and
+u = up(x) clamped to +-limit."""
 from __future__ import annotations
 
 import torch
@@ -12,7 +14,7 @@ from .registry import register_feed_forward
 
 class GatedMLP(FeedForward):
     """params: hidden_size, intermediate_size, activation (on the gate: one of ``ops.GATE_ACTIVATIONS``, default "silu"),
-    names (optional overrides)."""
+    limit (the bound of "clamped_swish"), names (optional overrides)."""
 
     NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
 
@@ -24,6 +26,9 @@ class GatedMLP(FeedForward):
         if self.activation not in ops.GATE_ACTIVATIONS:
             raise ValueError(f"feed-forward '{self.prefix}': unknown gate activation '{self.activation}'; known: "
                              f"{', '.join(ops.GATE_ACTIVATIONS)}")
+        self.limit = float(spec.params.get("limit", 0.0) or 0.0)
+        if self.activation == "clamped_swish" and not self.limit > 0:
+            raise ValueError(f"feed-forward '{self.prefix}': the clamped gate needs a positive 'limit', got {self.limit}")
         self.names = {**self.NAMES, **dict(spec.params.get("names", {}))}
         self.w_gate_up = self.w_down = None
         self.interleave = 0
@@ -53,7 +58,7 @@ class GatedMLP(FeedForward):
     adds_to_residual = True
 
     def forward(self, x, ctx, residual=None):
-        act = linear_swiglu(x, self.w_gate_up, self.runtime.dtype, self.interleave, self.activation)
+        act = linear_swiglu(x, self.w_gate_up, self.runtime.dtype, self.interleave, self.activation, self.limit)
         if residual is not None:
             return linear_onto(act, self.w_down, residual)  # None: the residual sum was made in the product's epilogue
         return linear(act, self.w_down)

@@ -43,6 +43,11 @@ class RMSNorm(Norm):
         """h += y / rms(y) * w in place (32-bit); the new h in ``cast_dtype`` if one is given."""
         return ops.rmsnorm_onto(h, y, self.weight, self.eps, cast_dtype)
 
+    def norm_sum(self, h, y, alpha=1.0, cast_dtype=None):
+        """h <- norm(alpha * h + y) * w in place (32-bit): the norm after the sum; the new h in ``cast_dtype`` if one is
+        given."""
+        return ops.rmsnorm_mix(h, y, self.weight, self.eps, alpha, cast_dtype)
+
 
 class LayerNorm(Norm):
     """Layer norm with a weight and no bias: (v - mean) / sqrt(var + eps) * w, var the mean of the squared deviations,

@@ -1,6 +1,7 @@
 """Mixers that carry a state of fixed size from token to token instead of keys and values: the state-space
-recurrence of Mamba-2, the gated delta rule with a decay per key channel, gated linear attention (the same decay, a plain
-outer-product write), and the recurrent block around a real-gated linear recurrent unit (one number of state per channel).  All keep, per sequence, a 32-bit
+recurrence of Mamba-2, the gated delta rule with a decay per key channel or per head, gated linear attention (a decay per
+key channel, a plain outer-product write), retention (the same write with a fixed decay per head and rotated queries and
+keys), and the recurrent block around a real-gated linear recurrent unit (one number of state per channel).  All keep, per sequence, a 32-bit
 state matrix per head and the last inputs of a short causal convolution, in the cache's per-slot state rows; a
 prompt and a single token run through the same kernels (``csrc/recurrent.cu``).  The projections are matrix
 products in the engine's dtype with 32-bit results; everything between them is 32-bit.
@@ -295,7 +296,148 @@ class GatedLinearAttentionMixer(Mixer):
         return linear(g, self.w_out)
 
 
+class GatedDeltaHeadMixer(Mixer):
+    """The gated delta rule with ONE decay per head.  q and k (``key_heads`` heads of ``key_dim``) and v (``heads`` heads
+    of ``vdim``) each pass a causal convolution (no bias) and SiLU; q and k become unit vectors per head
+    (x / sqrt(sum x^2 + ``unit_eps``)), q times key_dim^-1/2; beta = sigmoid(W_b h); g = exp(-exp(A_log_h) *
+    softplus(W_a h + dt_bias_h)) per head.  Per head (its q/k head is h // (heads / key_heads)):
+    S = g S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q.  Each head's o is RMS-normed over vdim, times a weight
+    shared by the heads, times silu(W_g h) (heads x vdim); then the output projection.
+
+    params: hidden_size, heads, key_heads, key_dim, vdim, conv (taps), norm_eps, unit_eps (default 1e-6), names.
+    State per sequence: the convolutions' last taps - 1 inputs and S, stored [heads, vdim, key_dim]."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "beta": "b",
+             "A_log": "A_log", "decay": "a", "dt_bias": "dt_bias", "gate": "g", "norm": "norm", "out": "o"}
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.key_heads = int(p["heads"]), int(p["key_heads"])
+        self.key_dim, self.vdim, self.taps = int(p["key_dim"]), int(p["vdim"]), int(p["conv"])
+        self.eps, self.unit_eps = float(p["norm_eps"]), float(p.get("unit_eps", 1e-6))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        if self.heads % self.key_heads:
+            raise ValueError(f"gated delta rule '{self.prefix}': {self.heads} heads are not a multiple of "
+                             f"{self.key_heads} query/key heads")
+        for refusal in (conv_taps_refusal(self.taps), state_matrix_refusal(self.key_dim, self.vdim)):
+            if refusal:
+                raise ValueError(f"gated delta rule '{self.prefix}': {refusal}")
+        self.n_qk = self.key_heads * self.key_dim
+        self.n_v = self.heads * self.vdim
+        self.channels = 2 * self.n_qk + self.n_v
+
+    def tensors(self):
+        n, px, D, H = self.names, self.prefix, self.hidden, self.heads
+        return [TensorSpec(px + n["q"], (self.n_qk, D), MATRIX), TensorSpec(px + n["q_conv"], (self.n_qk, self.taps), VECTOR),
+                TensorSpec(px + n["k"], (self.n_qk, D), MATRIX), TensorSpec(px + n["k_conv"], (self.n_qk, self.taps), VECTOR),
+                TensorSpec(px + n["v"], (self.n_v, D), MATRIX), TensorSpec(px + n["v_conv"], (self.n_v, self.taps), VECTOR),
+                TensorSpec(px + n["beta"], (H, D), MATRIX), TensorSpec(px + n["A_log"], (H,), VECTOR),
+                TensorSpec(px + n["norm"], (self.vdim,), VECTOR, NORM_WEIGHT),
+                TensorSpec(px + n["decay"], (H, D), MATRIX), TensorSpec(px + n["dt_bias"], (H,), VECTOR),
+                TensorSpec(px + n["gate"], (self.n_v, D), MATRIX), TensorSpec(px + n["out"], (D, self.n_v), MATRIX)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        # one projection for everything that reads the mixer's input: q | k | v | beta | decay | gate
+        self.w_in = torch.cat([take_weight(weights, px + n[k]) for k in ("q", "k", "v", "beta", "decay", "gate")], dim=0).contiguous()
+        self.conv_w = torch.cat([_f32(weights, px + n[k]) for k in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        self.w_out = weights[px + n["out"]]
+        self.a_log, self.dt_bias, self.norm_w = (_f32(weights, px + n[k]) for k in ("A_log", "dt_bias", "norm"))
+
+    def kernel_modules(self):
+        return ("recurrent", "elementwise", *linear_modules(self.runtime.dtype))
+
+    def state_spec(self):
+        state = StateSpec((self.heads, self.vdim, self.key_dim), torch.float32)       # column by column
+        return (StateSpec((self.taps - 1, self.channels), torch.float32), state) if self.taps > 1 else state
+
+    def forward(self, x, ctx, cache):
+        dtype, C, H = self.runtime.dtype, self.channels, self.heads
+        if self.taps > 1:
+            tail, state = cache.state
+        else:
+            tail, state = x.new_zeros((1, 0, C), dtype=torch.float32), cache.state
+        proj = linear(x, self.w_in)
+        qkv = ops.short_conv(proj, 0, C, self.conv_w, None, tail, ctx, update_tail=cache.writable)
+        o = ops.delta_rule(qkv, proj, C, proj, self.dt_bias, self.a_log, state, ctx, H, self.key_heads, self.key_dim,
+                           self.vdim, self.unit_eps, self.key_dim ** -0.5, write_state=cache.writable, per_head=True,
+                           a_col0=C + H)
+        g = ops.gated_part_norm(o, proj, C + 2 * H, self.norm_w, H, self.eps, gate_first=False, out_dtype=dtype,
+                                gate_activation="silu")
+        return linear(g, self.w_out)
+
+
+class RetentionMixer(Mixer):
+    """Linear attention with a fixed decay per head and neither softmax nor denominator.  q = W_q h and k = W_k h
+    (heads x key_dim), v = W_v h (heads x vdim); the position encoding turns the first part of every head of q and k
+    (value i with value i + n/2); k times ``k_scale`` after the turn.  Per head S <- decay_h S + k v^T from S = 0 and
+    o = S^T q.  Each head's o is divided by its root mean square over vdim (no weight), multiplied by silu(W_g h), and
+    projected by W_o.  The turn, the state, the read-out and the norm are 32-bit.
+
+    params: hidden_size, heads, key_dim, vdim, decay (one number per head), norm_eps, k_scale (default key_dim^-1/2),
+    names (optional overrides).  ``position``: an encoding that gives cos and sin [T, n/2], or None.
+    State per sequence: S, stored [heads, vdim, key_dim]."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o"}
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.key_dim, self.vdim = int(p["heads"]), int(p["key_dim"]), int(p["vdim"])
+        self.decays = [float(d) for d in p["decay"]]
+        self.eps = float(p["norm_eps"])
+        self.k_scale = float(p.get("k_scale", self.key_dim ** -0.5))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        self.position = position[0] if isinstance(position, (tuple, list)) else position
+        self.rotary_dim = getattr(self.position, "rotary_dim", 0) if self.position is not None else 0
+        if len(self.decays) != self.heads:
+            raise ValueError(f"retention '{self.prefix}': {len(self.decays)} decays for {self.heads} heads")
+        if self.rotary_dim > self.key_dim:
+            raise ValueError(f"retention '{self.prefix}': rotary size {self.rotary_dim} exceeds the key size {self.key_dim}")
+        refusal = state_matrix_refusal(self.key_dim, self.vdim)
+        if refusal:
+            raise ValueError(f"retention '{self.prefix}': {refusal}")
+        self.n_qk, self.n_v = self.heads * self.key_dim, self.heads * self.vdim
+
+    def tensors(self):
+        n, px, D = self.names, self.prefix, self.hidden
+        return [TensorSpec(px + n["q"], (self.n_qk, D), MATRIX), TensorSpec(px + n["k"], (self.n_qk, D), MATRIX),
+                TensorSpec(px + n["v"], (self.n_v, D), MATRIX), TensorSpec(px + n["gate"], (self.n_v, D), MATRIX),
+                TensorSpec(px + n["out"], (D, self.n_v), MATRIX)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        # one projection for everything that reads the mixer's input: q | k | v | gate
+        self.w_in = torch.cat([take_weight(weights, px + n[k]) for k in ("q", "k", "v", "gate")], dim=0).contiguous()
+        self.w_out = weights[px + n["out"]]
+        dev = self.w_out.device
+        self.decay = torch.tensor(self.decays, dtype=torch.float32, device=dev)
+        self.ones = torch.ones((self.vdim,), dtype=torch.float32, device=dev)
+
+    def kernel_modules(self):
+        return ("recurrent", "elementwise", *linear_modules(self.runtime.dtype))
+
+    def state_spec(self):
+        return StateSpec((self.heads, self.vdim, self.key_dim), torch.float32)       # column by column
+
+    def forward(self, x, ctx, cache):
+        proj = linear(x, self.w_in)
+        cos = sin = None
+        if self.position is not None and self.rotary_dim:
+            cos, sin = self.position.prepare(ctx)
+        o = ops.retention_scan(proj, cos, sin, self.rotary_dim, self.decay, cache.state, ctx, self.heads, self.key_dim,
+                               self.vdim, 1.0, self.k_scale, write_state=cache.writable)
+        g = ops.gated_part_norm(o, proj, 2 * self.n_qk + self.n_v, self.ones, self.heads, self.eps, gate_first=False,
+                                out_dtype=self.runtime.dtype, gate_activation="silu")
+        return linear(g, self.w_out)
+
+
 register_mixer("mamba2", Mamba2Mixer)
+register_mixer("gated_delta_headwise", GatedDeltaHeadMixer)
+register_mixer("retention", RetentionMixer)
 register_mixer("rglru", RGLRUMixer)
 register_mixer("gated_delta_channelwise", GatedDeltaMixer)
 register_mixer("gated_linear_attention", GatedLinearAttentionMixer)

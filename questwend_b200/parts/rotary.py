@@ -12,7 +12,8 @@ from .registry import register_position
 
 
 class RotaryEncoding(PositionEncoding):
-    """params: theta, rotary_dim."""
+    """params: theta, rotary_dim, linear_factor (every frequency is divided by it: positions shrink by that factor;
+    default 1)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -20,8 +21,11 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = int(spec.params["rotary_dim"])
         if self.rotary_dim <= 0 or self.rotary_dim % 2:
             raise ValueError(f"rotary size {self.rotary_dim} must be positive and even")
+        self.linear_factor = float(spec.params.get("linear_factor", 1.0) or 1.0)
+        if not self.linear_factor > 0:
+            raise ValueError(f"rotary scaling factor {self.linear_factor} must be positive")
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-        self.inv_freq = (self.theta ** (-2.0 * i / self.rotary_dim)).to(runtime.device)
+        self.inv_freq = (self.theta ** (-2.0 * i / self.rotary_dim) / self.linear_factor).to(runtime.device)
 
     def kernel_modules(self):
         return ("rope_kv",)
