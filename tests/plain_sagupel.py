@@ -98,8 +98,8 @@ def retention(h, m, w, px, eps, round16=False):
 
 def softmax_attention(h, m, w, px, eps, round16=False, biases=False, rotation=False, softcap=False, temp=False, talk=False,
                       gate=False, slopes=False, sink=False):
-    """Grouped-query attention without a value projection: the raw key projections serve as values.  The switches say which of the design's two
-    attentions this is."""
+    """Grouped-query attention without a value projection: the raw key projections serve as values.  The switches say
+    which of the design's two attentions this is."""
     n = h.shape[0]
     H, G, K = m["heads"], m["kv_heads"], m["dim"]
     q = product(h, w[px + "q"], round16)
@@ -109,7 +109,7 @@ def softmax_attention(h, m, w, px, eps, round16=False, biases=False, rotation=Fa
     q, k = q.reshape(n, H, K), k.reshape(n, G, K)
     v = k.copy()
     q, k = rms_norm(q, w[px + "q.norm"], eps), rms_norm(k, w[px + "k.norm"], eps)
-    if rotation:
+    if rotation and m.get("rot"):
         rot = m["rot"]
         factor = (rot.get("scaling") or {}).get("factor", 1.0)
         pos = np.arange(n)
@@ -126,7 +126,7 @@ def softmax_attention(h, m, w, px, eps, round16=False, biases=False, rotation=Fa
         s = (q[:, hd] @ k[:, hd // (H // G)].T) * m["scale"]
         if temp:
             s = s * w[px + "temp"][hd]
-        if softcap:
+        if softcap and m.get("softcap"):
             s = m["softcap"] * np.tanh(s / m["softcap"])
         if slopes:
             s = s - 2.0 ** (-8.0 * (hd + 1) / H) * (i - j)
@@ -197,11 +197,11 @@ def feed_forward(x, mlp, w, px, round16=False):
 # ----------------------------------------------------------------------------- the model
 def forward(cfg, w, tokens, round16=False, taps=None):
     """Logits [n, vocab] of one sequence; ``taps``, a list, receives the stream after every layer."""
-    eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
+    eps, alpha = cfg["norm"]["eps"], cfg.get("postln_alpha", 1.0)
     x = rms_norm(w["embed"][np.asarray(tokens)], w["embed.norm"], eps)
     for i, layer in enumerate(cfg["layers"]):
         px = f"l{i}."
-        h = causal_conv(x, w[px + "canon1"], plus_input=True)
+        h = causal_conv(x, w[px + "canon1"], plus_input=True) if cfg.get("canon") else x
         x = rms_norm(alpha * x + MIXERS[layer["type"]](h, layer["mixer"], w, px + "mix.", eps, round16), w[px + "norm1"], eps)
         if layer.get("mlp") is not None:
             x = rms_norm(alpha * x + feed_forward(x, layer["mlp"], w, px + "mlp.", round16), w[px + "norm2"], eps)
