@@ -107,6 +107,28 @@ def punolix_sizes(width=2048, repeats=2, chunk=1024, vocab=32768):
             "residual_mult": 0.7, "vocab": vocab, "width": width}
 
 
+def sagupel_sizes(width=2048, repeats=2, window=1024, vocab=32768):
+    """A Sagupel configuration at sizes that resemble real layers: per repeat a retention layer (16 heads of 128 x 128, all
+    of q and k turned), a layer with two mixers side by side (attention with capped scores, a number per head, mixed heads
+    and a gate per head, 16 heads of 128 over 4 key/value heads, beside the gated delta rule with a decay per head, 16
+    heads of 128 x 128 over 4 query/key heads, 4 taps) and an attention layer over a window of 1,024 positions with a
+    distance bias and a sink (16 heads of 128 over 4 key/value heads), each behind an input convolution of 3 taps and
+    with a clamped gated feed-forward of 3 x width."""
+    mlp = {"kind": "dense", "ff": 3 * width, "limit": 7.0}
+    heads = width // 128
+    ret = {"type": "retention", "mlp": mlp,
+           "mixer": {"decay": [1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)], "dim": 128, "heads": heads, "vdim": 128,
+                     "rot": {"base": 1000000.0, "dims": 128}}}
+    left = {"dim": 128, "heads": heads, "kv_heads": width // 512, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0}}}
+    right = {"conv": 4, "dim": 128, "heads": heads, "kv_heads": width // 512, "vdim": 128}
+    pair = {"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right}}
+    win = {"type": "attention", "mlp": mlp,
+           "mixer": {"dim": 128, "heads": heads, "kv_heads": width // 512, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window}}}
+    return {"architecture": "Sagupel", "canon": {"taps": 3}, "layers": [ret, pair, win] * repeats, "norm": {"eps": 1e-5},
+            "postln_alpha": 2.0, "vocab": vocab, "width": width}
+
+
 def qwen3_beside(width=2048, layers=6, vocab=32768):
     """The closest model the library had, at the same width, depth and vocabulary: Qwen3 layers with 16 heads of 128
     (8 key/value heads) and a gated feed-forward of 3 x width."""
@@ -665,6 +687,139 @@ def punolix_kernels(torch, np, peaks) -> dict:
     return out
 
 
+def sagupel_kernels(torch, np, peaks) -> dict:
+    """The Sagupel design's own kernels alone at the sizes of ``sagupel_sizes``, each beside the like kernel of a model the
+    library had, with the bytes or FLOPs it must move and the share of the measured peak that this comes to: attention over
+    a window with a distance bias and a sink, and attention with capped scores and mixed heads, in prompts of 2,048 and
+    8,192 tokens and in decode steps (beside Qwen3's attention and Punolix's capped attention with two score maps), the
+    preparation of q and k, retention and the delta rule with a decay per head (beside the delta rule with a decay per
+    channel), the norm after the sum (beside the norm in front of it) and the input convolution."""
+    from questwend_b200.cache.manager import CacheManager
+    from questwend_b200.engine.engine import StepEntry, build_step_context
+    from questwend_b200.kernels import ops
+    from questwend_b200.parts.base import KVSpec, StateSpec
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=7):
+        times = []
+        for _ in range(reps + 3):
+            flush.zero_()                                         # L2 holds nothing of the last run
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times[3:])
+
+    def point(us, n_bytes=0, flops=0):
+        p = {"us": round(us, 1)}
+        if n_bytes:
+            p.update(gb_s=round(n_bytes / us / 1e3, 1), hbm_frac=round(n_bytes / (us * 1e-6) / hbm, 3))
+        if flops:
+            p.update(tflops=round(flops / us / 1e6, 1), tensor_frac=round(flops / (us * 1e-6) / tf, 3))
+        return p
+
+    out = {}
+    H, G, window, cap = 16, 4, 1024, 30.0
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+    sinks, temp = torch.zeros(H, device=dev), torch.ones(H, device=dev)
+    mix = (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, device=dev)).contiguous()
+    for label, n_new, B, prompt in (("prefill_2048", 2048, 1, 0), ("prefill_8192", 8192, 1, 0), ("decode_b8_at_4096", 1, 8, 4095),
+                                    ("decode_b8_at_32768", 1, 8, 32767)):
+        spec, two = KVSpec(G, 128, 0, value_dim=128), KVSpec(G, 2 * 64, 0, value_dim=128)
+        n_ctx = prompt + n_new
+        cache = CacheManager([(spec, None, None), (two, None, None)], B * n_ctx + 64 * B, B, n_ctx + 64, bf, dev)
+        slots = cache.open(B)
+        if prompt:
+            build_step_context(cache, [StepEntry(s, [0] * prompt, []) for s in slots], 10, dev)
+            for s in slots:
+                cache.advance(s, prompt)
+        u1, u2 = cache.unit_cache(0), cache.unit_cache(1)
+        for unit in (u1, u2):
+            unit.k_pool.normal_()
+            unit.v_pool.normal_()
+        ctx = build_step_context(cache, [StepEntry(s, [0] * n_new, []) for s in slots], 10, dev)[0]
+        rows = B * n_new
+        t1, t2 = ctx.page_tables[u1.group_id], ctx.page_tables[u2.group_id]
+        q1 = torch.randn(rows, H, 128, device=dev).to(bf)
+        q2 = torch.randn(rows, H, 2 * 64, device=dev).to(bf)
+        gate = torch.randn(rows, H, device=dev)
+        windowed = lambda: ops.bias_attention(q1, u1.k_pool, u1.v_pool, t1, ctx, 0.09, slopes=slopes, window=window, sinks=sinks)
+        mixed = lambda: ops.bias_attention(q1, u1.k_pool, u1.v_pool, t1, ctx, 0.09, head_scale=temp, softcap=cap, head_mix=mix, gate=gate)
+        capped = lambda: ops.bias_attention(q1, u1.k_pool, u1.v_pool, t1, ctx, 0.09, head_scale=temp, softcap=cap)
+        punolix = lambda: ops.maps_attention(q2, u2.k_pool, u2.v_pool, t2, ctx, 2, 0.125, softcap=50.0, lam=0.6, norm_out=True, eps=1e-5, out_scale=0.2)
+        if n_new > 1:       # per (query, visible key): 2 FLOPs per key value and 2 per value; mixed heads: the values of all G heads
+            full = n_new * (n_new + 1) // 2
+            seen = sum(min(p + 1, window) for p in range(n_new))
+            out[f"window_attention_{label}"] = point(timed(windowed, reps=3), flops=H * seen * 4 * 128)
+            out[f"mixed_heads_attention_{label}"] = point(timed(mixed, reps=3), flops=H * full * 2 * 128 * (1 + G))
+            out[f"capped_attention_no_mix_{label}"] = point(timed(capped, reps=3), flops=H * full * 4 * 128)
+            out[f"punolix_two_capped_maps_{label}"] = point(timed(punolix, reps=3), flops=H * full * 2 * (2 * 64 + 2 * 128))
+            for impl in ("tc", "mma"):
+                out[f"qwen3_attention_{impl}_{label}"] = point(timed(lambda: ops.attn_prefill(q1, u1.k_pool, u1.v_pool, t1, ctx.cu_seqlens, ctx.pos0, ctx.max_new, 0.09, impl=impl), reps=3),
+                                                               flops=H * full * 4 * 128)
+                out[f"qwen3_attention_{impl}_window_{window}_{label}"] = point(timed(lambda: ops.attn_prefill(q1, u1.k_pool, u1.v_pool, t1, ctx.cu_seqlens, ctx.pos0, ctx.max_new, 0.09, window=window, impl=impl), reps=3),
+                                                                               flops=H * seen * 4 * 128)
+        else:               # a decode step reads the visible keys and values of every key/value head once
+            inside = min(n_ctx, window)
+            out[f"window_attention_{label}"] = point(timed(windowed), B * G * inside * 2 * 128 * 2)
+            out[f"mixed_heads_attention_{label}"] = point(timed(mixed), B * G * n_ctx * 2 * 128 * 2)
+            out[f"capped_attention_no_mix_{label}"] = point(timed(capped), B * G * n_ctx * 2 * 128 * 2)
+            out[f"punolix_two_capped_maps_{label}"] = point(timed(punolix), B * G * n_ctx * (2 * 64 + 128) * 2)
+            out[f"qwen3_attention_{label}"] = point(timed(lambda: ops.attn_decode(q1, u1.k_pool, u1.v_pool, t1, ctx.seq_len, 0.09, ctx.max_len)),
+                                                    B * G * n_ctx * 2 * 128 * 2)
+            out[f"qwen3_attention_window_{window}_{label}"] = point(timed(lambda: ops.attn_decode(q1, u1.k_pool, u1.v_pool, t1, ctx.seq_len, 0.09, ctx.max_len, window=window)),
+                                                                    B * G * inside * 2 * 128 * 2)
+        # what stands in front of the scores: norm of q and k, rotation, cache write (float in, bfloat16 out); the values are the keys
+        n_cols = (H + G) * 128
+        qk = torch.randn(rows, n_cols, device=dev)
+        nw, cs = torch.ones(128, device=dev), torch.ones(rows, 64, device=dev)
+        out[f"bias_prep_{label}"] = point(timed(lambda: ops.bias_prep(qk, None, nw, nw, cs, cs, ctx, t1, u1.k_pool, u1.v_pool, H, G, 128, 128, 128, False, 1e-5, values_are_keys=True)),
+                                          rows * (n_cols * 4 + (H + 2 * G) * 128 * 2))
+        qkv = torch.randn(rows, n_cols + G * 128, device=dev)
+        out[f"punolix_maps_prep_{label}"] = point(timed(lambda: ops.maps_prep(qkv, None, nw, nw, cs, cs, ctx, t1, u1.k_pool, u1.v_pool, H, G, 1, 128, 128, 128, False, 1e-5)),
+                                                  rows * (n_cols + G * 128) * 6)
+        del cache, u1, u2
+        torch.cuda.empty_cache()
+    # the recurrences, 16 heads of 128 x 128: one prompt of 2,048 tokens, and a step of 8 single tokens
+    for rows, B in ((2048, 1), (8, 8)):
+        heads, K, P = 16, 128, 128
+        cache = CacheManager([(None, StateSpec((heads, P, K)), None)], 4096, 8, 4096, bf, dev)
+        slots = cache.open(B)
+        ctx = build_step_context(cache, [StepEntry(s, [0] * (rows // B), []) for s in slots], 10, dev)[0]
+        st = cache.unit_cache(0).state
+        moved = rows * heads * (2 * K + 2 * P) * 4 + (2 * B * st[0].numel() * 4 if rows == B else 0)
+        qkv = torch.randn(rows, heads * (2 * K + P), device=dev) * 0.1
+        cs = torch.ones(rows, 64, device=dev)
+        decay = torch.full((heads,), 0.98, device=dev)
+        out[f"retention_scan_{rows}"] = point(timed(lambda: ops.retention_scan(qkv, cs, cs, 128, decay, st, ctx, heads, K, P, 1.0, K ** -0.5)), moved)
+        proj = torch.randn(rows, 4 * K * 2 + heads * P + 2 * heads, device=dev) * 0.1
+        qkv4 = torch.randn(rows, 4 * K * 2 + heads * P, device=dev) * 0.1
+        C = 4 * K * 2 + heads * P
+        dt_bias, a_log = torch.zeros(heads, device=dev), torch.zeros(heads, device=dev)
+        out[f"delta_rule_decay_per_head_{rows}"] = point(timed(lambda: ops.delta_rule(qkv4, proj, C, proj, dt_bias, a_log, st, ctx, heads, 4, K, P, 1e-6, K ** -0.5, per_head=True, a_col0=C + heads)),
+                                                         rows * (2 * 4 * K + heads * P * 2) * 4 + (2 * B * st[0].numel() * 4 if rows == B else 0))
+        qkv2 = torch.randn(rows, heads * (2 * K + P), device=dev) * 0.1
+        b_raw, a_raw2 = torch.randn(rows, heads, device=dev), torch.randn(rows, heads * K, device=dev)
+        dt_bias2 = torch.zeros(heads * K, device=dev)
+        out[f"delta_rule_decay_per_channel_{rows}"] = point(timed(lambda: ops.delta_rule(qkv2, b_raw, 0, a_raw2, dt_bias2, a_log, st, ctx, heads, heads, K, P, 1e-6, K ** -0.5)),
+                                                            rows * heads * (3 * K + 2 * P) * 4 + (2 * B * st[0].numel() * 4 if rows == B else 0))
+        # the stream's kernels at width 2,048
+        D = 2048
+        h, y, w = torch.randn(rows, D, device=dev), torch.randn(rows, D, device=dev), torch.ones(D, device=dev)
+        out[f"norm_after_the_sum_{rows}"] = point(timed(lambda: ops.rmsnorm_mix(h, y, w, 1e-5, 2.0, bf)), rows * D * 14)
+        out[f"norm_before_with_its_sum_{rows}"] = point(timed(lambda: ops.rmsnorm(h, w, 1e-5, bf, delta=y, write_sum=True)), rows * D * 14)
+        tail = torch.zeros(8, 2, D, device=dev)
+        cw = torch.randn(D, 3, device=dev)
+        out[f"input_convolution_{rows}"] = point(timed(lambda: ops.short_conv(h, 0, D, cw, None, tail, ctx, activation=False, plus_input=True, out_dtype=bf)), rows * D * 6)
+        del cache
+        torch.cuda.empty_cache()
+    return out
+
+
 def reference_arm(args) -> int:
     """kishida/questwend itself, unmodified, through its own public classes (baseline/ref_bench.cpp), on the same sizes.
     Nothing of questwend_b200 is imported on this path."""
@@ -757,9 +912,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--model", default="8b", choices=sorted(MODELS) + ["movudra", "roritar", "roritar-kernels", "punolix", "punolix-kernels"],
-                    help="8b: the benchmark; 0.6b, 32b: its other workloads alone; movudra, roritar, punolix: that design at real layer "
-                         "sizes beside Qwen3 layers of the same width and depth; roritar-kernels, punolix-kernels: its own kernels alone, each "
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS) + ["movudra", "roritar", "roritar-kernels", "punolix", "punolix-kernels", "sagupel", "sagupel-kernels"],
+                    help="8b: the benchmark; 0.6b, 32b: its other workloads alone; movudra, roritar, punolix, sagupel: that design at real layer "
+                         "sizes beside Qwen3 layers of the same width and depth; roritar-kernels, punolix-kernels, sagupel-kernels: its own kernels alone, each "
                          "beside the like kernel of a model the library had")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -810,6 +965,17 @@ def main() -> int:
         print(json.dumps({"metric": "Punolix's kernels alone, each beside the like kernel of an earlier model", "n_gpus": 1,
                           "dtype": "bf16", "data": "synthetic: random tensors of the sizes of punolix_sizes; L2 flushed between runs",
                           "peaks": peak_source, "points": punolix_kernels(torch, np, peaks)}))
+        return 0
+    if args.model == "sagupel":
+        designs = (("sagupel", sagupel_sizes()), ("punolix_same_size", punolix_sizes()), ("qwen3_same_size", qwen3_beside()))
+        print(json.dumps({"metric": "Sagupel at real layer sizes beside Punolix and Qwen3 layers of equal width and depth", "n_gpus": 1,
+                          "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
+                          "peaks": peak_source, "points": movudra_workload(torch, np, peaks, steps, warmup, designs)}))
+        return 0
+    if args.model == "sagupel-kernels":
+        print(json.dumps({"metric": "Sagupel's kernels alone, each beside the like kernel of an earlier model", "n_gpus": 1,
+                          "dtype": "bf16", "data": "synthetic: random tensors of the sizes of sagupel_sizes; L2 flushed between runs",
+                          "peaks": peak_source, "points": sagupel_kernels(torch, np, peaks)}))
         return 0
     if args.model != "8b":                      # one of the other workloads alone, as a line of its own
         points = small_model_workload(torch, np, peaks) if args.model == "0.6b" else large_model_workload(torch, np, peaks)

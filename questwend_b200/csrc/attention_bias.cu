@@ -16,6 +16,7 @@
 //                  rdims values of every head of q and k, cache write of a step's tokens (the values may be the keys as
 //                  projected, before norm and rotation); q out
 //   bias_prefill   any number of new tokens per sequence (float and bfloat16, any sizes up to 256)
+//   bias_prefill_mma  bfloat16 prompts on the tensor cores
 //   bias_decode    one new token per sequence: runs of pages, one block of threads a run, then bias_merge, which also adds
 //                  the sink
 //   bias_head_mix  the mix of the heads and the gate
@@ -281,6 +282,291 @@ extern "C" int qwb_bias_prefill(const void* q, const void* k_pool, const void* v
     if (dtype == QWB_DT_BF16) return raw_out ? QWB_BIAS_PF(bf16, float) : QWB_BIAS_PF(bf16, bf16);
 #undef QWB_BIAS_PF
     return qwb_fail(QWB_ERR_ARG, "bias_prefill: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------
+// prefill on the tensor cores (bfloat16, mma.sync m16n8k16): block = 64 queries of one (sequence, query head, value
+// head), 4 warps of 16 rows; keys in tiles of 64 = one page of the cache, from the page of the first key that the tile's
+// first query sees to the page of its last query.  Q, K and V tiles sit in shared memory with rows padded by 16 bytes
+// (conflict-free ldmatrix); K has two buffers, V one: the next tile's keys are copied in (cp.async) under this tile's work,
+// its values under its own scores and softmax.  Scores, the cap, the distance bias, maxima, sums, the sink and the
+// accumulators are 32-bit; probabilities are rounded to bfloat16 for the second product.  dim a multiple of 16, vdim of 8.
+// ---------------------------------------------------------------------------------
+#define BM_BQ 64
+#define BM_BK 64
+#define BM_PAD 8
+
+__device__ __forceinline__ void bm_ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void bm_ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void bm_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 16 bytes from global to shared memory; `bytes` 0 writes zeros (src must still be a valid address)
+__device__ __forceinline__ void bm_cp16(bf16* dst, const bf16* src, int bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void bm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t bm_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bm_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float bm_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void bm_store2(bf16* p, float a, float b) { *reinterpret_cast<uint32_t*>(p) = bm_pack(a, b); }
+__device__ __forceinline__ void bm_store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+// 16-byte pieces of a [rows][cpr pieces] tile, dealt to 128 threads in order: the thread's first piece and its stride,
+// as (row, piece) pairs, so that the copy loops divide nothing
+struct BmWalk {
+    int r0, c0, dr, dc, cpr;
+    __device__ __forceinline__ BmWalk(int tid, int pieces_per_row) : r0(tid / pieces_per_row), c0(tid % pieces_per_row),
+        dr(128 / pieces_per_row), dc(128 % pieces_per_row), cpr(pieces_per_row) {}
+    __device__ __forceinline__ void next(int& r, int& c) const { r += dr; c += dc; if (c >= cpr) { c -= cpr; ++r; } }
+};
+
+template <int NV, typename TO>     // n-tiles of 8 value columns the accumulator has room for; the output's type
+__global__ void __launch_bounds__(128)
+bias_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        const int* __restrict__ page_table, const int* __restrict__ cu_seqlens, const int* __restrict__ pos0,
+                        TO* __restrict__ out, int H, int G, int C, int dim, int vdim, int table_width, float scale,
+                        const float* __restrict__ head_scale, float softcap, const float* __restrict__ slopes, int window,
+                        const float* __restrict__ sinks) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int ldq = dim + BM_PAD, ldv = vdim + BM_PAD;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);           // [64][ldq]
+    bf16* Kbuf = Qs + BM_BQ * ldq;                          // [2][64][ldq]
+    bf16* Vbuf = Kbuf + 2 * BM_BK * ldq;                    // [64][ldv]
+
+    // the last queries see the most keys: their blocks start first, so that the long blocks are not the launch's tail
+    const int b = blockIdx.z, h = blockIdx.y / C, c = blockIdx.y % C, q0 = (int)(gridDim.x - 1 - blockIdx.x) * BM_BQ;
+    const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+    if (q0 >= n) return;
+    const int g_kv = h / (H / G), g_v = C > 1 ? c : g_kv;
+    const int p0 = pos0[b];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nq = min(BM_BQ, n - q0);
+    const int gr = lane >> 2, tq = lane & 3;
+    const int pos_a = p0 + q0 + warp * 16 + gr, pos_b = pos_a + 8;  // positions of the thread's two rows
+    const int lo_a = bias_first_key(pos_a, window), lo_b = bias_first_key(pos_b, window);
+
+    const int k_hi = p0 + q0 + nq - 1;                              // last key any query of the tile sees
+    const int k_lo = bias_first_key(p0 + q0, window);               // first key any of them sees
+    const int nv_used = vdim / 8;
+    const int first_page = k_lo / BM_BK, n_tiles = k_hi / BM_BK - first_page + 1;
+    const int* pages = page_table + (size_t)b * table_width;
+    const int warp_lo = p0 + q0 + warp * 16, warp_hi = warp_lo + 15;
+    const int warp_first = bias_first_key(warp_hi, window);         // the first key that every row of the warp may see
+    const float log2e = 1.4426950408889634f;
+    // Scores in units of ln 2 (ex2 below).  With a cap c: c tanh(x / c) = c - 2 c / (e^(2 x / c) + 1), exact at both ends
+    // (e^.. = inf or 0) and a few units of the last place in between: one ex2, one rcp and one fma a score.
+    const float hs = scale * (head_scale ? head_scale[h] : 1.f);
+    const float mul_s = softcap > 0.f ? hs / softcap * 2.f * log2e : hs * log2e;
+    const float cap2 = softcap * log2e;
+    const float slope2 = slopes ? slopes[h] * log2e : 0.f;
+    const BmWalk walk_k(tid, dim / 8), walk_v(tid, vdim / 8);
+
+    auto copy_keys = [&](int it, int stage) {                   // one commit group
+        const int page = first_page + it;
+        const int rows = min(BM_BK, k_hi + 1 - page * BM_BK);
+        const bf16* ks = k_pool + ((size_t)pages[page] * G + g_kv) * BM_BK * dim;
+        bf16* Kd = Kbuf + stage * BM_BK * ldq;
+        for (int r = walk_k.r0, cc = walk_k.c0; r < BM_BK; walk_k.next(r, cc))
+            bm_cp16(Kd + r * ldq + cc * 8, ks + (size_t)(r < rows ? r : 0) * dim + cc * 8, r < rows ? 16 : 0);
+        bm_commit();
+    };
+    auto copy_values = [&](int it) {                            // one commit group
+        const int page = first_page + it;
+        const int rows = min(BM_BK, k_hi + 1 - page * BM_BK);
+        const bf16* vs = v_pool + ((size_t)pages[page] * G + g_v) * BM_BK * vdim;
+        for (int r = walk_v.r0, cc = walk_v.c0; r < BM_BK; walk_v.next(r, cc))
+            bm_cp16(Vbuf + r * ldv + cc * 8, vs + (size_t)(r < rows ? r : 0) * vdim + cc * 8, r < rows ? 16 : 0);
+        bm_commit();
+    };
+    for (int r = walk_k.r0, cc = walk_k.c0; r < BM_BQ; walk_k.next(r, cc)) {
+        const bool in = r < nq;
+        bm_cp16(Qs + r * ldq + cc * 8, q + ((size_t)(t0 + (in ? q0 + r : 0)) * H + h) * dim + cc * 8, in ? 16 : 0);
+    }
+    // groups in the order of their commits: [Q, K0], V0, K1, V1, K2, ...
+    copy_keys(0, 0);
+    copy_values(0);
+
+    float o[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows gr and gr + 8 of the warp's 16
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const bf16* Ks = Kbuf + (it & 1) * BM_BK * ldq;
+        const bf16* Vs = Vbuf;
+        const bool more = it + 1 < n_tiles;
+        if (more) {                                             // the next keys into the other buffer (its last readers
+            copy_keys(it + 1, (it + 1) & 1);                    // passed the barrier at the end of the round before)
+            bm_wait<2>();                                       // this tile's keys (and Q) are there
+        } else {
+            bm_wait<1>();
+        }
+        __syncthreads();
+        const int key0 = (first_page + it) * BM_BK;
+        // a tile that no row of the warp sees (behind its last row, or before its window) is skipped by the warp
+        const bool none = key0 > warp_hi || key0 + BM_BK <= bias_first_key(warp_lo, window);
+        float s[8][4];
+        if (!none) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            for (int d = 0; d < dim; d += 16) {
+                uint32_t a0, a1, a2, a3;
+                bm_ldsm_x4(a0, a1, a2, a3, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldq + d + (lane >> 4) * 8);
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {                // two tiles of 8 keys a load
+                    uint32_t b0, b1, b2, b3;
+                    bm_ldsm_x4(b0, b1, b2, b3, Ks + (j * 8 + (lane & 7) + (lane >> 4) * 8) * ldq + d + ((lane >> 3) & 1) * 8);
+                    bm_mma(s[j], a0, a1, a2, a3, b0, b1);
+                    bm_mma(s[j + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+            // a tile that every row of the warp sees whole needs no mask (most tiles of a long prompt)
+            const bool whole = key0 + BM_BK - 1 <= warp_lo && key0 >= warp_first;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + tq * 2 + (e & 1);
+                    bool ok = true;
+                    if (!whole) ok = key <= (e < 2 ? pos_a : pos_b) && key >= (e < 2 ? lo_a : lo_b) && key <= k_hi;
+                    float v = s[j][e] * mul_s;
+                    if (softcap > 0.f) v = fmaf(-2.f * cap2, bm_rcp(bm_ex2(v) + 1.f), cap2);
+                    v = fmaf(-slope2, (float)((e < 2 ? pos_a : pos_b) - key), v);
+                    s[j][e] = ok ? v : -INFINITY;
+                }
+                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float alpha0 = bm_ex2(m0 - base0), alpha1 = bm_ex2(m1 - base1);  // m = -inf gives 0
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                s[j][0] = bm_ex2(s[j][0] - base0); s[j][1] = bm_ex2(s[j][1] - base0);
+                s[j][2] = bm_ex2(s[j][2] - base1); s[j][3] = bm_ex2(s[j][3] - base1);
+                sum0 += s[j][0] + s[j][1];
+                sum1 += s[j][2] + s[j][3];
+            }
+            sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+            sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+            l0 = l0 * alpha0 + sum0; l1 = l1 * alpha1 + sum1;
+            m0 = mn0; m1 = mn1;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) { o[j][0] *= alpha0; o[j][1] *= alpha0; o[j][2] *= alpha1; o[j][3] *= alpha1; }
+        }
+
+        if (more) bm_wait<1>(); else bm_wait<0>();              // this tile's values are there
+        __syncthreads();
+        if (!none) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {                    // O += P V, 16 keys a step
+                const uint32_t a0 = bm_pack(s[2 * ks][0], s[2 * ks][1]), a1 = bm_pack(s[2 * ks][2], s[2 * ks][3]);
+                const uint32_t a2 = bm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), a3 = bm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+                for (int j = 0; j < NV; j += 2) {
+                    if (j < nv_used) {                          // vdim / 8 may be odd: the second tile of a pair reads padding
+                        uint32_t b0, b1, b2, b3;                // or the next row's start, and its result is never stored
+                        bm_ldsm_x4_trans(b0, b1, b2, b3, Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + j * 8 + (lane >> 4) * 8);
+                        bm_mma(o[j], a0, a1, a2, a3, b0, b1);
+                        if (j + 1 < NV) bm_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                        // the values' buffer may be copied into again
+        if (more) copy_values(it + 1);
+    }
+
+    float mul0 = 1.f, mul1 = 1.f;
+    if (sinks) {                                                // one more term of the denominator
+        const float sk = sinks[h] * log2e;
+        const float n0 = fmaxf(m0, sk), n1 = fmaxf(m1, sk);
+        mul0 = bm_ex2(m0 - n0); mul1 = bm_ex2(m1 - n1);
+        l0 = l0 * mul0 + bm_ex2(sk - n0); l1 = l1 * mul1 + bm_ex2(sk - n1);
+    }
+    const float inv0 = l0 > 0.f ? mul0 / l0 : 0.f, inv1 = l1 > 0.f ? mul1 / l1 : 0.f;
+    const int row_a = warp * 16 + gr, row_b = row_a + 8;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        if (j < nv_used) {
+            const int col = j * 8 + tq * 2;
+            if (row_a < nq) bm_store2(out + (((size_t)(t0 + q0 + row_a) * H + h) * C + c) * vdim + col, o[j][0] * inv0, o[j][1] * inv0);
+            if (row_b < nq) bm_store2(out + (((size_t)(t0 + q0 + row_b) * H + h) * C + c) * vdim + col, o[j][2] * inv1, o[j][3] * inv1);
+        }
+    }
+}
+
+// Q and two key buffers [64][dim + 8] and one value buffer [64][vdim + 8] of bfloat16
+static size_t bm_smem_bytes(int dim, int vdim) {
+    return ((size_t)3 * BM_BK * (dim + BM_PAD) + (size_t)BM_BK * (vdim + BM_PAD)) * sizeof(bf16);
+}
+
+extern "C" int qwb_bias_prefill_mma_fits(int dtype, int dim, int vdim) {
+    return dtype == QWB_DT_BF16 && dim > 0 && dim % 16 == 0 && vdim > 0 && vdim % 8 == 0 && dim <= QWB_BIAS_MAX_DIM &&
+           vdim <= QWB_BIAS_MAX_DIM && bm_smem_bytes(dim, vdim) <= 220 * 1024;
+}
+
+// q [T, H, dim] bfloat16; out [T, H, C, vdim] as for the plain kernel.
+extern "C" int qwb_bias_prefill_mma(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
+                                    const int* pos0, void* out, int raw_out, int B, int max_new, int H, int G, int all_values, int dim,
+                                    int vdim, int table_width, float scale, const float* head_scale, float softcap, const float* slopes,
+                                    int window, const float* sinks, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    if (int rc = check_bias_sizes("bias_prefill_mma", H, G, dim, vdim, table_width, window, 8)) return rc;
+    if (!qwb_bias_prefill_mma_fits(QWB_DT_BF16, dim, vdim))
+        return qwb_fail(QWB_ERR_ARG, "bias_prefill_mma: keys of %d (a multiple of 16) and values of %d (of 8) that fit in shared memory", dim, vdim);
+    const int C = all_values ? G : 1;
+    if (all_values && !raw_out) return qwb_fail(QWB_ERR_ARG, "bias_prefill_mma: the outputs for all value heads are 32-bit");
+    if (B > 65535 || H * C > 65535) return qwb_fail(QWB_ERR_ARG, "bias_prefill_mma: batch %d or heads %d above 65535", B, H * C);
+    for (const void* p : {q, k_pool, v_pool, (const void*)out})
+        if ((uintptr_t)p % 16) return qwb_fail(QWB_ERR_ARG, "bias_prefill_mma: a tensor is not 16-byte aligned");
+    const size_t smem = bm_smem_bytes(dim, vdim);
+    const dim3 grid((max_new + BM_BQ - 1) / BM_BQ, H * C, B);
+#define QWB_BM(NV, TO)                                                                                                          \
+    do {                                                                                                                        \
+        if (smem > 48 * 1024) {                                                                                                 \
+            cudaError_t e = cudaFuncSetAttribute(bias_prefill_mma_kernel<NV, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "bias_prefill_mma: %s", cudaGetErrorString(e));                 \
+        }                                                                                                                       \
+        qwb_launch(bias_prefill_mma_kernel<NV, TO>, grid, 128, smem, stream, (const bf16*)q, (const bf16*)k_pool,               \
+                   (const bf16*)v_pool, page_table, cu_seqlens, pos0, (TO*)out, H, G, C, dim, vdim, table_width, scale, head_scale, \
+                   softcap, slopes, window, sinks);                                                                             \
+    } while (0)
+#define QWB_BM_SIZES(TO)                                                                                                        \
+    do {                                                                                                                        \
+        if (vdim <= 32) QWB_BM(4, TO); else if (vdim <= 64) QWB_BM(8, TO); else if (vdim <= 128) QWB_BM(16, TO);                \
+        else QWB_BM(32, TO);                                                                                                    \
+    } while (0)
+    if (raw_out) QWB_BM_SIZES(float); else QWB_BM_SIZES(bf16);
+#undef QWB_BM_SIZES
+#undef QWB_BM
+    return qwb_check_launch("bias_prefill_mma");
 }
 
 // ---------------------------------------------------------------------------------

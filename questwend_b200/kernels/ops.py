@@ -1237,6 +1237,15 @@ def maps_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, maps: int, 
 # ----------------------------------------------------------------------------- attention with shaped scores
 BIAS_ATTN_MAX_DIM = 256     # csrc/attention_bias.cu: QWB_BIAS_MAX_DIM
 BIAS_ATTN_FAST_STEP = 8     # key and value sizes that are multiples of this take the kernels that copy 16 bytes at a time
+BIAS_PREFILL_MMA = True     # bfloat16 prompts take the tensor-core kernel where it fits; False: always the plain one
+BIAS_MMA_MIN_NEW = 16       # ... from this many new tokens of the longest sequence on (a tile is 64 queries)
+
+
+def bias_prefill_mma_fits(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """Whether prompts take the tensor-core kernel: bfloat16, keys in multiples of 16, values of 8, tiles that fit."""
+    if dtype != torch.bfloat16 or not BIAS_PREFILL_MMA:
+        return False
+    return bool(_lookup("attention_bias", "qwb_bias_prefill_mma_fits")[1](_i(DT_BF16), _i(dim), _i(vdim)))
 
 
 def bias_prep(qkv: torch.Tensor, bias, q_weight, k_weight, cos, sin, ctx, page_table, k_pool, v_pool, n_heads: int,
@@ -1275,7 +1284,8 @@ def bias_prep(qkv: torch.Tensor, bias, q_weight, k_weight, cos, sin, ctx, page_t
 
 
 def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: float, head_scale=None, softcap: float = 0.0,
-                   slopes=None, window: int = 0, sinks=None, head_mix=None, gate=None, gate_col0: int = 0) -> torch.Tensor:
+                   slopes=None, window: int = 0, sinks=None, head_mix=None, gate=None, gate_col0: int = 0,
+                   impl: str = "auto") -> torch.Tensor:
     """Softmax attention of a step's tokens with scores shaped head by head.  ``q`` [T, H, dim] in the cache's dtype;
     returns [T, H * vdim] in that dtype.  score = q . k * ``scale`` * ``head_scale``[h]; capped (``softcap`` > 0:
     c tanh(s / c)); minus ``slopes``[h] times the key's distance from the query; causal, and within the last ``window``
@@ -1283,7 +1293,8 @@ def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: floa
     the heads' weights are mixed after the softmax, w'_h = sum_g mix[h, g] w_g, each head still reading its own value
     head.  ``gate``: head h's output times sigmoid of column ``gate_col0 + h`` of the float32 matrix ``gate`` [T, ld].
     The per-head vectors are float32 [H].  Steps of one token per sequence take the kernel that cuts the keys into runs
-    (sizes that are multiples of 8), other steps the plain prompt kernel."""
+    (sizes that are multiples of 8); other steps the tensor-core kernel where it fits (``impl`` "auto"; "mma": always),
+    else the plain prompt kernel ("plain")."""
     _need(q, "q", k_pool.dtype, 3)
     T, H, dim = q.shape
     G, vdim = k_pool.shape[1], v_pool.shape[3]
@@ -1318,6 +1329,11 @@ def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: floa
               _ptr(scratch), _ptr(att), _i(_dt(q.dtype)), _i(1 if raw else 0), _i(T), _i(H), _i(G), _i(1 if all_values else 0),
               _i(dim), _i(vdim), _i(width), _f(scale), _ptr(head_scale), _f(softcap), _ptr(slopes), _i(window), _ptr(sinks),
               _i(n_runs), _stream(), kernels=2)
+    elif impl == "mma" or (impl == "auto" and ctx.max_new >= BIAS_MMA_MIN_NEW and bias_prefill_mma_fits(q.dtype, dim, vdim)):
+        _call("attention_bias", "qwb_bias_prefill_mma", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
+              _ptr(ctx.pos0), _ptr(att), _i(1 if raw else 0), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G),
+              _i(1 if all_values else 0), _i(dim), _i(vdim), _i(width), _f(scale), _ptr(head_scale), _f(softcap), _ptr(slopes),
+              _i(window), _ptr(sinks), _stream())
     else:
         _call("attention_bias", "qwb_bias_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
               _ptr(ctx.pos0), _ptr(att), _i(_dt(q.dtype)), _i(1 if raw else 0), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G),

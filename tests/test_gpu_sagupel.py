@@ -391,6 +391,84 @@ def test_the_sink_takes_its_share():
     assert np.abs(outs["high"]).max() < 1e-6 * np.abs(outs["low"]).max()
 
 
+# ----------------------------------------------------------------------------- the prompt kernel on the tensor cores
+def shaped_oracle(q, k, v, pos0, scale, head_scale, softcap, slopes, window, sinks, mix, gate):
+    """q [n, H, dim], k [L, G, dim], v [L, G, vdim] of one sequence (float64); the n queries sit at pos0 .. pos0 + n - 1.
+    Returns [n, H * vdim]."""
+    n, H, L, G = q.shape[0], q.shape[1], k.shape[0], k.shape[1]
+    i, j = np.arange(pos0, pos0 + n)[:, None], np.arange(L)[None, :]
+    seen = (j <= i) & ((i - j < window) if window > 0 else True)
+    weights = np.zeros((H, n, L))
+    for h in range(H):
+        s = q[:, h] @ k[:, h // (H // G)].T * scale * (head_scale[h] if head_scale is not None else 1.0)
+        if softcap > 0:
+            s = softcap * np.tanh(s / softcap)
+        if slopes is not None:
+            s = s - slopes[h] * (i - j)
+        s = np.where(seen, s, -np.inf)
+        top = s.max(-1, keepdims=True)
+        if sinks is not None:
+            top = np.maximum(top, sinks[h])
+        e = np.exp(s - top)
+        weights[h] = e / (e.sum(-1, keepdims=True) + (np.exp(sinks[h] - top) if sinks is not None else 0.0))
+    if mix is not None:
+        weights = np.einsum("hg,gij->hij", mix, weights)
+    out = np.stack([weights[h] @ v[:, h // (H // G)] for h in range(H)], axis=1)
+    if gate is not None:
+        out = out * ps.sigmoid(gate)[:, :, None]
+    return out.reshape(n, -1)
+
+
+@pytest.mark.parametrize("H, G, dim, vdim, window, extras", [
+    (4, 2, 64, 64, 0, "cap temp mix gate"), (8, 4, 32, 32, 0, "mix"), (4, 1, 96, 96, 136, "slopes sink"), (2, 2, 16, 24, 70, "slopes sink cap"),
+    (6, 2, 128, 128, 64, "sink"), (3, 1, 48, 8, 1, "slopes"), (2, 1, 256, 256, 0, "gate"), (5, 5, 16, 40, 200, "temp slopes sink mix gate cap")])
+def test_prompt_kernels_and_the_decode_kernel_against_an_oracle(H, G, dim, vdim, window, extras):
+    """Random queries and a random cache: unequal prompts whole and as later portions (queries that start at a position
+    above 0, inside a page), and single tokens, on the tensor cores and on the plain kernels."""
+    rng = np.random.default_rng(H * 1000 + dim)
+    spec = __import__("questwend_b200.parts.base", fromlist=["KVSpec"]).KVSpec(G, dim, window, value_dim=vdim)
+    lens, new = [300, 70, 17, 1], [[300, 70, 17, 1], [121, 70, 3, 1], [1, 1, 1, 1]]
+    head_scale = f32(1 + 0.4 * rng.standard_normal(H)) if "temp" in extras else None
+    slopes = f32([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)]) if "slopes" in extras else None
+    sinks = f32(1 + rng.standard_normal(H)) if "sink" in extras else None
+    mix = f32(np.eye(H) + 0.4 * rng.standard_normal((H, H))) if "mix" in extras else None
+    softcap = 3.0 if "cap" in extras else 0.0
+    for dtype in DTYPES:
+        cache = CacheManager([(spec, None, None)], sum(lens) + 64 * 5, 4, 400, dtype, DEV)
+        unit = cache.unit_cache(0)
+        ks = [ps.round_bf16(rng.standard_normal((n, G, dim))) for n in lens]
+        vs = [ps.round_bf16(rng.standard_normal((n, G, vdim))) for n in lens]
+        for counts in new:
+            slots = cache.open(4)
+            before = [n - c for n, c in zip(lens, counts)]
+            for s, n in zip(slots, before):
+                if n:
+                    build_step_context(cache, [StepEntry(s, [0] * n, [])], 10, DEV)
+                    cache.advance(s, n)
+            ctx = build_step_context(cache, [StepEntry(s, [0] * c, []) for s, c in zip(slots, counts)], 10, DEV)[0]
+            table = ctx.page_tables[unit.group_id].cpu().numpy()
+            for b, (k, v) in enumerate(zip(ks, vs)):                 # the cache as a prep kernel would have left it
+                for p in range(lens[b]):
+                    unit.k_pool[table[b, p // 64], :, p % 64] = dev(k[p], dtype)
+                    unit.v_pool[table[b, p // 64], :, p % 64] = dev(v[p], dtype)
+            qs = [ps.round_bf16(rng.standard_normal((c, H, dim))) for c in counts]
+            gates = [f32(rng.standard_normal((c, H))) for c in counts] if "gate" in extras else None
+            want = np.concatenate([shaped_oracle(q, k, v, n0, 0.3, head_scale, softcap, slopes, window, sinks, mix,
+                                                 None if gates is None else gates[b])
+                                   for b, (q, k, v, n0) in enumerate(zip(qs, ks, vs, before))])
+            gate = None if gates is None else dev(np.concatenate([np.zeros((sum(counts), 3)), np.concatenate(gates)], axis=1))
+            impls = ["auto"] if ctx.single_token else (["plain", "mma"] if dtype == torch.bfloat16 and dim % 16 == 0 else ["plain"])
+            for impl in impls:
+                got = ops.bias_attention(dev(np.concatenate(qs), dtype), unit.k_pool, unit.v_pool, ctx.page_tables[unit.group_id], ctx, 0.3,
+                                         head_scale=None if head_scale is None else dev(head_scale), softcap=softcap,
+                                         slopes=None if slopes is None else dev(slopes), window=window,
+                                         sinks=None if sinks is None else dev(sinks), head_mix=None if mix is None else dev(mix),
+                                         gate=gate, gate_col0=3, impl=impl).double().cpu().numpy()
+                tol = 1e-4 if dtype == torch.float32 else 0.02
+                assert np.abs(got - want).max() <= tol * max(np.abs(want).max(), 1.0), (dtype, counts, impl)
+            cache.close(slots)
+
+
 # ----------------------------------------------------------------------------- whole models
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
