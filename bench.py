@@ -424,7 +424,11 @@ def time_parts(engine, torch, rng, n_tokens: int, batch: int, prompt: int = 0, r
     for i, run in enumerate(engine.model.schedule):
         block = engine.model.blocks[run.layer]
         unit = engine.unit_caches[i]
-        name = type(block.mixer).__name__
+        mixer = block.mixer
+        name = type(mixer).__name__
+        if hasattr(mixer, "inner"):                             # a mixer behind an input convolution: named by what it wraps
+            inner = mixer.inner
+            name = "+".join(type(m).__name__ for m in getattr(inner, "branches", [inner])) + "_behind_conv"
         if name not in seen:
             seen.add(name)
             if getattr(block.mixer, "adds_to_residual", False):

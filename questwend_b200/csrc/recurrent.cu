@@ -451,7 +451,7 @@ extern "C" int qwb_turn_qk_prep(float* qkv, int ld, float* kq, const float* cos_
 // linear attention, S = decay[:, None] * S + k v^T.  The decays of token t, head h: decay_k = K values at decay +
 // t * decay_ts + h * K (one per key channel), or decay_k = 1 value at decay + t * decay_ts + h (one per head; with
 // decay_ts = 0 the same H numbers for every token: a fixed decay per head).
-template <int PER, bool VEC, int TB, int CW>
+template <int PER, bool VEC, int TB, int CW, bool PC>     // PC: a decay per key channel (else one per head)
 __global__ void __launch_bounds__(32 * QWB_SCAN_WARPS)
 delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ kq, const float* __restrict__ beta,
                   const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ cu_seqlens,
@@ -463,7 +463,6 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
     const int p0 = (blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5)) * CW, h = blockIdx.y, b = blockIdx.z;
     if (p0 >= P) return;                                            // P is a multiple of CW: a warp's columns all exist
     const int kh = h / (H / Hk);
-    const bool per_channel = decay_k > 1 || K == 1;
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     const int n0 = lane * PER;
     float* S = state + (((size_t)slots[b] * H + h) * P + p0) * K;
@@ -474,7 +473,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
     // TB tokens a round: their vectors are asked for together (once for the warp's CW columns) and a round ahead of
     // their use (and into L2 some rounds earlier); the state then runs through a round's tokens in order (a token's
     // write needs the sum over the rows of the token before it), the columns side by side
-    float kn[TB][PER], qn[TB][PER], gn[TB][PER], v_n[TB][CW], bt_n[TB], kq_n[TB];
+    float kn[TB][PER], qn[TB][PER], gn[TB][PC ? PER : 1], v_n[TB][CW], bt_n[TB], kq_n[TB];
     auto load_round = [&](int tc) {
 #pragma unroll
         for (int j = 0; j < TB; ++j) {
@@ -482,12 +481,8 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
             const float* row = qkv + (size_t)t * ld;
             load_rows<PER, VEC>(row + kh * K, n0, K, qn[j]);
             load_rows<PER, VEC>(row + (Hk + kh) * K, n0, K, kn[j]);
-            if (per_channel) load_rows<PER, VEC>(decay + (size_t)t * decay_ts + h * K, n0, K, gn[j]);
-            else {
-                const float one = decay[(size_t)t * decay_ts + h];
-#pragma unroll
-                for (int k = 0; k < PER; ++k) gn[j][k] = one;
-            }
+            if (PC) load_rows<PC ? PER : 1, PC && VEC>(decay + (size_t)t * decay_ts + h * K, n0, K, gn[j]);
+            else gn[j][0] = decay[(size_t)t * decay_ts + h];
 #pragma unroll
             for (int c = 0; c < CW; ++c) v_n[j][c] = row[v_at + c];
             bt_n[j] = beta ? beta[(size_t)t * H + h] : 0.f; kq_n[j] = kq[(size_t)t * Hk + kh];
@@ -495,12 +490,14 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
     };
     if (t0 < t1) load_round(t0);
     for (int tc = t0; tc < t1; tc += TB) {
-        float kk[TB][PER], qq[TB][PER], gg[TB][PER], v[TB][CW], bt[TB], kqv[TB];
+        float kk[TB][PER], qq[TB][PER], gg[TB][PC ? PER : 1], v[TB][CW], bt[TB], kqv[TB];
 #pragma unroll
         for (int j = 0; j < TB; ++j) {
             bt[j] = bt_n[j]; kqv[j] = kq_n[j];
 #pragma unroll
-            for (int k = 0; k < PER; ++k) { kk[j][k] = kn[j][k]; qq[j][k] = qn[j][k]; gg[j][k] = gn[j][k]; }
+            for (int k = 0; k < PER; ++k) { kk[j][k] = kn[j][k]; qq[j][k] = qn[j][k]; }
+#pragma unroll
+            for (int k = 0; k < (PC ? PER : 1); ++k) gg[j][k] = gn[j][k];
 #pragma unroll
             for (int c = 0; c < CW; ++c) v[j][c] = v_n[j][c];
         }
@@ -512,7 +509,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
                 const float* row = qkv + (size_t)t * ld;
                 prefetch_l2(row + kh * K + n0);
                 prefetch_l2(row + (Hk + kh) * K + n0);
-                if (per_channel) prefetch_l2(decay + (size_t)t * decay_ts + h * K + n0);
+                if (PC) prefetch_l2(decay + (size_t)t * decay_ts + h * K + n0);
                 if (lane == 0) prefetch_l2(row + v_at);
             }
         }
@@ -525,7 +522,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
                     sk[c] = sq[c] = 0.f;
 #pragma unroll
                     for (int k = 0; k < PER; ++k) {
-                        s[c][k] *= gg[j][k];
+                        s[c][k] *= gg[j][PC ? k : 0];
                         sk[c] += s[c][k] * kk[j][k];
                         sq[c] += s[c][k] * qq[j][k];
                     }
@@ -566,12 +563,15 @@ extern "C" int qwb_delta_scan(const float* qkv, int ld, const float* kq, const f
     int cw = per <= 4 && P % 4 == 0 ? 4 : (per <= 8 && P % 2 == 0 ? 2 : 1);            // columns a warp, as in ssm_scan
     if (cw > QWB_DELTA_CW_MAX) cw = QWB_DELTA_CW_MAX;
     const dim3 grid((P / cw + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
-#define QWB_DELTA1(PER, VEC, CW) qwb_launch(delta_scan_kernel<PER, VEC, (PER <= 4 ? 4 : (PER == 8 ? 2 : 1)), CW>, grid, 32 * QWB_SCAN_WARPS, 0, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state, decay_ts, decay_k)
+    const bool pc = decay_k > 1 || K == 1;
+#define QWB_DELTA0(PER, VEC, CW, PC) qwb_launch(delta_scan_kernel<PER, VEC, (PER <= 4 ? 4 : (PER == 8 ? 2 : 1)), CW, PC>, grid, 32 * QWB_SCAN_WARPS, 0, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state, decay_ts, decay_k)
+#define QWB_DELTA1(PER, VEC, CW) do { if (pc) QWB_DELTA0(PER, VEC, CW, true); else QWB_DELTA0(PER, VEC, CW, false); } while (0)
 #define QWB_DELTA(PER, VEC) do { if (cw == 4 && PER <= 4) QWB_DELTA1(PER, VEC, (PER <= 4 ? 4 : 1)); else if (cw >= 2 && PER <= 8) QWB_DELTA1(PER, VEC, (PER <= 8 ? 2 : 1)); else QWB_DELTA1(PER, VEC, 1); } while (0)
     if (per == 1) QWB_DELTA(1, false); else if (per == 2) QWB_DELTA(2, false);
     else if (per == 4) { if (vec) QWB_DELTA(4, true); else QWB_DELTA(4, false); }
     else if (per == 8) { if (vec) QWB_DELTA(8, true); else QWB_DELTA(8, false); }
     else { if (vec) QWB_DELTA(16, true); else QWB_DELTA(16, false); }
+#undef QWB_DELTA0
 #undef QWB_DELTA1
 #undef QWB_DELTA
     return qwb_check_launch("delta_scan");

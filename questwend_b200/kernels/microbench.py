@@ -14,6 +14,7 @@ move, and GB/s.  Also the program to put under ncu for a capture of one kernel o
 from __future__ import annotations
 
 import argparse
+import sys
 import json
 import math
 import statistics
@@ -251,9 +252,49 @@ def bench_maps_attention(B, tokens, ctx, Hq, Hkv, maps, dim, vdim, softcap, chun
             "gb_s_of_visible_rows": (B * Hkv * (seen / tokens) * (maps * dim + vdim) * q.element_size() / us / 1e3) if tokens == 1 else None}
 
 
+def bench_shaped_attention(B, tokens, ctx, Hq, Hkv, dim, softcap, window, extras, iters, dtype=torch.bfloat16, impl="auto") -> dict:
+    """Attention with shaped scores: ``B`` sequences that bring ``tokens`` new tokens each after ``ctx`` cached ones (tokens = 1:
+    the decode kernels; more: a prompt kernel).  ``extras``: words out of "slopes sink temp mix gate".  Random queries, keys and
+    values; keys and values of one size."""
+    from ..cache.manager import CacheManager
+    from ..engine.engine import StepEntry, build_step_context
+    from ..parts.base import KVSpec
+    n = ctx + tokens
+    cache = CacheManager([(KVSpec(Hkv, dim, window, value_dim=dim), None, None)], B * n + 64 * B, B, n + 64, dtype, DEV)
+    slots = cache.open(B)
+    if ctx:
+        build_step_context(cache, [StepEntry(s, [0] * ctx, []) for s in slots], 10, DEV)
+        for s in slots:
+            cache.advance(s, ctx)
+    unit = cache.unit_cache(0)
+    unit.k_pool.normal_()
+    unit.v_pool.normal_()
+    step = build_step_context(cache, [StepEntry(s, [0] * tokens, []) for s in slots], 10, DEV)[0]
+    q = torch.randn(B * tokens, Hq, dim, device=DEV).to(dtype)
+    table = step.page_tables[unit.group_id]
+    kw = {"softcap": softcap, "window": window, "impl": impl}
+    if "slopes" in extras:
+        kw["slopes"] = torch.tensor([2.0 ** (-8.0 * (h + 1) / Hq) for h in range(Hq)], device=DEV)
+    if "sink" in extras:
+        kw["sinks"] = torch.zeros(Hq, device=DEV)
+    if "temp" in extras:
+        kw["head_scale"] = torch.ones(Hq, device=DEV)
+    if "mix" in extras:
+        kw["head_mix"] = (torch.eye(Hq, device=DEV) + 0.1 * torch.randn(Hq, Hq, device=DEV)).contiguous()
+    if "gate" in extras:
+        kw["gate"] = torch.randn(B * tokens, Hq, device=DEV)
+    us = _time(lambda i: ops.bias_attention(q, unit.k_pool, unit.v_pool, table, step, dim ** -0.5, **kw), 1, iters, burst=3)
+    seen = sum(min(p + 1, window) if window else p + 1 for p in range(ctx, n))
+    value_heads = Hkv if "mix" in extras else 1
+    return {"what": "shaped_attention", "batch": B, "tokens": tokens, "ctx": ctx, "heads": Hq, "kv_heads": Hkv, "dim": dim,
+            "softcap": softcap, "window": window, "extras": extras, "impl": impl, "us": us,
+            "tflops_of_visible_keys": 2 * B * Hq * dim * (1 + value_heads) * seen / us / 1e6,
+            "gb_s_of_visible_rows": (B * Hkv * (seen / tokens) * 2 * dim * q.element_size() / us / 1e3) if tokens == 1 else None}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "rope", "decode_shapes", "sample", "pool_attn", "maps_attn"])
+    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "rope", "decode_shapes", "sample", "pool_attn", "maps_attn", "shaped_attn"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -283,6 +324,7 @@ def main() -> int:
     ap.add_argument("--chunk", type=int, default=0, help="maps_attn: positions per chunk (0: plain causal)")
     ap.add_argument("--attn-impl", default="auto", choices=["auto", "tc", "mma", "plain"], help="maps_attn: the prompt kernel")
     ap.add_argument("--pool", type=int, default=16, help="pool_attn: tokens per pooled block")
+    ap.add_argument("--extras", default="", help="shaped_attn: words out of 'slopes sink temp mix gate'")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     if args.what == "gemm":
@@ -303,6 +345,10 @@ def main() -> int:
         print(json.dumps(bench_maps_attention(args.batch, args.tokens, args.ctx if args.tokens == 1 else 0, args.heads, args.kv_heads,
                                               args.maps, args.head_dim, args.value_dim or args.head_dim, args.softcap, args.chunk,
                                               args.iters, dtype, args.attn_impl)))
+    elif args.what == "shaped_attn":
+        print(json.dumps(bench_shaped_attention(args.batch, args.tokens, args.ctx if args.tokens == 1 else 0, args.heads, args.kv_heads,
+                                                args.head_dim, args.softcap, args.window if "--window" in sys.argv else 0, args.extras,
+                                                args.iters, dtype, args.attn_impl)))
     elif args.what == "sample":
         print(json.dumps(bench_sample(args.batch, args.vocab, args.temp, args.top_k, args.top_p, args.iters)))
     elif args.what == "attn_prefill":
