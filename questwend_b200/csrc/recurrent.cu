@@ -578,6 +578,192 @@ extern "C" int qwb_delta_scan(const float* qkv, int ld, const float* kq, const f
 }
 
 // ---------------------------------------------------------------------------------
+// Linear attention with a FIXED decay per head over long prompts, in chunks of 64 tokens.  The recurrence
+// S <- d S + k v^T, o = S^T q is linear in S, so with S0 the state at a chunk's start and i, j tokens of the chunk
+//     o_i = d^(i+1) S0^T q_i + sum_{j <= i} d^(i-j) (q_i . k_j) v_j,      S_end = d^n S0 + sum_j d^(n-1-j) k_j v_j^T
+// and chunks compose exactly up to rounding.  Three kernels, all 32-bit: every chunk's own sum of outer products from
+// a zero state (chunk_state), the carries through a sequence's chunks in order, which leave each chunk's S0 in the
+// scratch and the final state in the cache (chunk_carry), and the chunks' outputs (chunk_out).  A chunk is a block, so
+// a prompt of 2,048 tokens and 16 heads is 512 blocks instead of a chain of 2,048 steps.  The powers of d are made in
+// 64-bit.  qkv [T, ld]: q [H * K] | k [H * K] | v [H * P], already turned and scaled; scratch [B * chunks, H, P, K].
+// ---------------------------------------------------------------------------------
+#define QWB_CHUNK 64
+
+// grid (chunks, H, B), 256 threads; dynamic shared memory: QWB_CHUNK * (K + P + 1) floats
+__global__ void __launch_bounds__(256)
+retention_chunk_state_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
+                             float* __restrict__ scratch, int H, int K, int P, int n_chunks) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float cs_smem[];
+    const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int t0 = cu_seqlens[b] + c * QWB_CHUNK, t1 = min(cu_seqlens[b + 1], t0 + QWB_CHUNK);
+    if (t0 >= t1) return;
+    const int n = t1 - t0;
+    float* ks = cs_smem;                    // [n][K]
+    float* vs = ks + QWB_CHUNK * K;         // [n][P], times d^(n - 1 - j)
+    float* pw = vs + QWB_CHUNK * P;         // [QWB_CHUNK] powers of the decay
+    const double d = (double)decay[h];
+    for (int i = threadIdx.x; i < QWB_CHUNK; i += blockDim.x) pw[i] = (float)pow(d, (double)i);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n * K; idx += blockDim.x) {
+        const int j = idx / K, k = idx - j * K;
+        ks[idx] = qkv[(size_t)(t0 + j) * ld + (H + h) * K + k];
+    }
+    for (int idx = threadIdx.x; idx < n * P; idx += blockDim.x) {
+        const int j = idx / P, p = idx - j * P;
+        vs[idx] = qkv[(size_t)(t0 + j) * ld + 2 * H * K + h * P + p] * pw[n - 1 - j];
+    }
+    __syncthreads();
+    float* U = scratch + (((size_t)b * n_chunks + c) * H + h) * (size_t)P * K;
+    const int K4 = K >> 2;
+    for (int idx = threadIdx.x; idx < P * K4; idx += blockDim.x) {
+        const int p = idx / K4, k4 = idx - p * K4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < n; ++j) {
+            const float4 kk = *reinterpret_cast<const float4*>(ks + j * K + 4 * k4);
+            const float v = vs[j * P + p];
+            acc.x += kk.x * v; acc.y += kk.y * v; acc.z += kk.z * v; acc.w += kk.w * v;
+        }
+        *reinterpret_cast<float4*>(U + (size_t)p * K + 4 * k4) = acc;
+    }
+}
+
+// grid (ceil(P * K / 256), H, B): every element of the state runs through its sequence's chunks in order
+__global__ void retention_chunk_carry_kernel(const float* __restrict__ decay, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                                             float* __restrict__ state, float* scratch, int H, int K, int P, int n_chunks, int write_state) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y, b = blockIdx.z;
+    if (e >= P * K) return;
+    const int n_tok = cu_seqlens[b + 1] - cu_seqlens[b];
+    if (n_tok <= 0) return;
+    const double d = (double)decay[h];
+    const float d_full = (float)pow(d, (double)QWB_CHUNK);
+    float* S = state + ((size_t)slots[b] * H + h) * (size_t)P * K + e;
+    float s = *S;
+    const int chunks = (n_tok + QWB_CHUNK - 1) / QWB_CHUNK;
+    for (int c = 0; c < chunks; ++c) {
+        float* U = scratch + (((size_t)b * n_chunks + c) * H + h) * (size_t)P * K + e;
+        const float own = *U;
+        *U = s;                                                     // the state this chunk starts from
+        const int n = min(QWB_CHUNK, n_tok - c * QWB_CHUNK);
+        s = (n == QWB_CHUNK ? d_full : (float)pow(d, (double)n)) * s + own;
+    }
+    if (write_state) *S = s;
+}
+
+// grid (chunks, H, B), 256 threads; dynamic shared memory: see retention_chunk_smem_floats
+__global__ void __launch_bounds__(256)
+retention_chunk_out_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
+                           const float* __restrict__ scratch, float* __restrict__ o, int H, int K, int P, int n_chunks) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int L = QWB_CHUNK, IB = 8;
+    extern __shared__ __align__(16) float co_smem[];
+    const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int t0 = cu_seqlens[b] + c * L, t1 = min(cu_seqlens[b + 1], t0 + L);
+    if (t0 >= t1) return;
+    const int n = t1 - t0, KP = K > P ? K : P;
+    float* qs = co_smem;                    // [L][K]
+    float* kv = qs + L * K;                 // [L][max(K, P)]: the keys, then the values
+    float* A = kv + L * KP;                 // [L][L + 1]
+    float* S0 = A + L * (L + 1);            // [P][K + 1]
+    float* pw = S0 + (size_t)P * (K + 1);   // [L + 1] powers of the decay
+    const double d = (double)decay[h];
+    for (int i = threadIdx.x; i <= L; i += blockDim.x) pw[i] = (float)pow(d, (double)i);
+    for (int idx = threadIdx.x; idx < n * K; idx += blockDim.x) {
+        const int j = idx / K, k = idx - j * K;
+        const float* row = qkv + (size_t)(t0 + j) * ld;
+        qs[j * K + k] = row[h * K + k];
+        kv[j * K + k] = row[(H + h) * K + k];
+    }
+    const float* S = scratch + (((size_t)b * n_chunks + c) * H + h) * (size_t)P * K;
+    for (int idx = threadIdx.x; idx < P * K; idx += blockDim.x) {
+        const int p = idx / K, k = idx - p * K;
+        S0[p * (K + 1) + k] = S[idx];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n * n; idx += blockDim.x) {      // A[i][j] = d^(i - j) q_i . k_j for j <= i
+        const int i = idx / n, j = idx - i * n;
+        float dot = 0.f;
+        if (j <= i) {
+            const float4* qa = reinterpret_cast<const float4*>(qs + i * K);
+            const float4* kb = reinterpret_cast<const float4*>(kv + j * K);
+            for (int k = 0; k < (K >> 2); ++k) {
+                const float4 x = qa[k], y = kb[k];
+                dot += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+            }
+            dot *= pw[i - j];
+        }
+        A[i * (L + 1) + j] = dot;
+    }
+    __syncthreads();                                                    // the keys are no longer read
+    for (int idx = threadIdx.x; idx < n * P; idx += blockDim.x) {
+        const int j = idx / P, p = idx - j * P;
+        kv[j * P + p] = qkv[(size_t)(t0 + j) * ld + 2 * H * K + h * P + p];
+    }
+    __syncthreads();
+    const int groups = (n + IB - 1) / IB;
+    for (int idx = threadIdx.x; idx < groups * P; idx += blockDim.x) {  // IB tokens of one value column a thread
+        const int ig = idx / P, p = idx - ig * P, i0 = ig * IB;
+        float acc[IB];
+#pragma unroll
+        for (int ii = 0; ii < IB; ++ii) acc[ii] = 0.f;
+        const float* srow = S0 + p * (K + 1);
+        for (int k = 0; k < K; ++k) {
+            const float sv = srow[k];
+#pragma unroll
+            for (int ii = 0; ii < IB; ++ii) acc[ii] += sv * qs[min(i0 + ii, n - 1) * K + k];
+        }
+#pragma unroll
+        for (int ii = 0; ii < IB; ++ii) acc[ii] *= pw[min(i0 + ii, n - 1) + 1];
+        const int j_end = min(i0 + IB, n);
+        for (int j = 0; j < j_end; ++j) {
+            const float v = kv[j * P + p];
+#pragma unroll
+            for (int ii = 0; ii < IB; ++ii) acc[ii] += A[min(i0 + ii, n - 1) * (L + 1) + j] * v;      // zero for j > i
+        }
+#pragma unroll
+        for (int ii = 0; ii < IB; ++ii)
+            if (i0 + ii < n) o[((size_t)(t0 + i0 + ii) * H + h) * P + p] = acc[ii];
+    }
+}
+
+static size_t retention_chunk_smem_floats(int K, int P) {
+    const int KP = K > P ? K : P;
+    return (size_t)QWB_CHUNK * K + (size_t)QWB_CHUNK * KP + (size_t)QWB_CHUNK * (QWB_CHUNK + 1) + (size_t)P * (K + 1) + QWB_CHUNK + 1;
+}
+
+// 1 if the chunked form takes these sizes (keys in multiples of 4, tiles that fit in shared memory)
+extern "C" int qwb_retention_chunked_fits(int K, int P) {
+    return K > 0 && P > 0 && K % 4 == 0 && retention_chunk_smem_floats(K, P) * sizeof(float) <= 200 * 1024;
+}
+
+extern "C" int qwb_retention_chunk_len() { return QWB_CHUNK; }
+
+// scratch: B * ceil(max_new / 64) * H * P * K floats
+extern "C" int qwb_retention_chunked(const float* qkv, int ld, const float* decay, float* state, const int* cu_seqlens, const int* slots,
+                                     float* scratch, float* o, int B, int max_new, int H, int K, int P, int write_state, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    if (H <= 0 || !qwb_retention_chunked_fits(K, P) || ld < H * (2 * K + P) || ld % 4 || (uintptr_t)qkv % 16 || (uintptr_t)scratch % 16)
+        return qwb_fail(QWB_ERR_ARG, "retention_chunked: %d heads of %d x %d in rows of %d", H, K, P, ld);
+    const int n_chunks = (max_new + QWB_CHUNK - 1) / QWB_CHUNK;
+    if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "retention_chunked: %d sequences or %d heads are too many", B, H);
+    const size_t smem1 = (size_t)QWB_CHUNK * (K + P + 1) * sizeof(float), smem3 = retention_chunk_smem_floats(K, P) * sizeof(float);
+    cudaError_t e = cudaSuccess;
+    if (smem1 > 48 * 1024) e = cudaFuncSetAttribute(retention_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (e == cudaSuccess && smem3 > 48 * 1024) e = cudaFuncSetAttribute(retention_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "retention_chunked: %s", cudaGetErrorString(e));
+    qwb_launch(retention_chunk_state_kernel, dim3(n_chunks, H, B), 256, smem1, stream, qkv, ld, decay, cu_seqlens, scratch, H, K, P, n_chunks);
+    if (int rc = qwb_check_launch("retention_chunk_state")) return rc;
+    qwb_launch(retention_chunk_carry_kernel, dim3((P * K + 255) / 256, H, B), 256, 0, stream, decay, cu_seqlens, slots, state, scratch, H, K, P, n_chunks, write_state);
+    if (int rc = qwb_check_launch("retention_chunk_carry")) return rc;
+    qwb_launch(retention_chunk_out_kernel, dim3(n_chunks, H, B), 256, smem3, stream, qkv, ld, decay, cu_seqlens, (const float*)scratch, o, H, K, P, n_chunks);
+    return qwb_check_launch("retention_chunk_out");
+}
+
+// ---------------------------------------------------------------------------------
 // Gated norm over equal parts of a row.  y [T, n_parts * part] float, gate: column slice of a [T, ld_gate] matrix.
 //   mode 0: v = y * silu(gate); out = v / rms(v over the part) * w      (the gate before the norm)
 //   mode 1: out = y / rms(y over the part) * w * sigmoid(gate)          (the gate after the norm)

@@ -906,15 +906,26 @@ def delta_rule(qkv: torch.Tensor, b_raw: torch.Tensor, b_col0: int, a_raw: torch
     return o
 
 
+RETENTION_CHUNK = 64            # tokens per chunk of the chunked form of retention (csrc/recurrent.cu: QWB_CHUNK) ...
+RETENTION_CHUNKED_FROM = 128    # ... which steps whose longest sequence brings at least this many tokens take
+
+
+def retention_chunked_fits(key_dim: int, vdim: int) -> bool:
+    """Whether the chunked form takes a state of key_dim x vdim per head (its tiles must fit in shared memory)."""
+    return bool(_lookup("recurrent", "qwb_retention_chunked_fits")[1](_i(key_dim), _i(vdim)))
+
+
 def retention_scan(qkv: torch.Tensor, cos, sin, rotary_dim: int, decay: torch.Tensor, state: torch.Tensor, ctx, heads: int,
-                   key_dim: int, vdim: int, q_scale: float, k_scale: float, write_state: bool = True) -> torch.Tensor:
+                   key_dim: int, vdim: int, q_scale: float, k_scale: float, write_state: bool = True,
+                   chunked: bool | None = None) -> torch.Tensor:
     """Linear attention with a fixed decay per head over a step's tokens: per head S = decay_h S + k v^T, o = S^T q.
     ``qkv`` float32 [T, ld] whose first 2 * heads * key_dim + heads * vdim columns are q | k | v; the first
     ``rotary_dim`` values of every head of q and k are turned by the tokens' angles (``cos``, ``sin`` float32
     [T, rotary_dim / 2]; value i with value i + rotary_dim / 2), then q is multiplied by ``q_scale`` and k by ``k_scale``,
     in place.  ``decay`` float32 [heads]; ``state`` float32 [slots, heads, vdim, key_dim] (column by column) is read and
     written back.  Returns o float32 [T, heads * vdim].  The recurrence is the delta rule's kernel without its correction
-    term."""
+    term; steps that bring long prompts (``chunked`` None: from ``RETENTION_CHUNKED_FROM`` tokens on) take the chunked
+    form instead, where its sizes fit."""
     _need(qkv, "qkv", torch.float32, 2)
     _need(state, "state", torch.float32, 4)
     _need(decay, "decay", torch.float32, 1)
@@ -935,6 +946,16 @@ def retention_scan(qkv: torch.Tensor, cos, sin, rotary_dim: int, decay: torch.Te
     _call("recurrent", "qwb_turn_qk_prep", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(cos), _ptr(sin), _i(T), _i(heads),
           _i(key_dim), _i(rotary_dim), _f(q_scale), _f(k_scale), _stream())
     o = torch.empty((T, heads * vdim), dtype=torch.float32, device=dev)
+    if chunked is None:
+        chunked = ctx.max_new >= RETENTION_CHUNKED_FROM
+    if chunked and qkv.shape[1] % 4 == 0 and retention_chunked_fits(key_dim, vdim):
+        # long prompts: chunks of 64 tokens side by side (three kernels) instead of a chain through every token
+        n_chunks = -(-ctx.max_new // RETENTION_CHUNK)
+        scratch = torch.empty((ctx.n_seqs * n_chunks, heads, vdim, key_dim), dtype=torch.float32, device=dev)
+        _call("recurrent", "qwb_retention_chunked", _ptr(qkv), _i(qkv.shape[1]), _ptr(decay), _ptr(state), _ptr(ctx.cu_seqlens),
+              _ptr(ctx.slots), _ptr(scratch), _ptr(o), _i(ctx.n_seqs), _i(ctx.max_new), _i(heads), _i(key_dim), _i(vdim),
+              _i(1 if write_state else 0), _stream(), kernels=3)
+        return o
     _call("recurrent", "qwb_delta_scan", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(None), _ptr(decay), _ptr(state),
           _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(o), _i(ctx.n_seqs), _i(heads), _i(heads), _i(key_dim), _i(vdim),
           _i(1 if write_state else 0), _i(0), _i(1), _stream())

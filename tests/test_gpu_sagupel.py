@@ -223,6 +223,34 @@ def test_retention_long_memory_in_portions_and_in_used_slots():
         assert close(run_mixer(part, dtype, [x], plan, cache=cache)[0], ref, dtype), plan[0]
 
 
+@pytest.mark.parametrize("entry", [sh.retention(heads=2, dim=16, vdim=24, dims=16, base=100.0, decay=(0.999, 0.99)),
+                                   sh.retention(heads=3, dim=64, vdim=32, dims=32, decay=(1.0, 0.5, 0.96875)),
+                                   sh.retention(heads=1, dim=128, vdim=128, dims=None, decay=(0.998,)),
+                                   sh.retention(heads=2, dim=12, vdim=5, dims=4, decay=(0.0, 0.9))])
+def test_retention_in_chunks_against_the_chain(entry):
+    """Long prompts take the chunked form (chunks of 64 tokens side by side): unequal prompts that end inside a chunk, a
+    portion that continues a state, and the state it leaves for the tokens after it, against the plain implementation and
+    against the kernel that runs through the tokens one by one."""
+    width, dtype = 32, torch.float32
+    w = sh.draw_weights(sh.config([(entry, None)], width=width), 4)
+    rng = np.random.default_rng(6)
+    lens = [333, 130, 64]
+    xs = [ps.round_bf16(rng.standard_normal((n + 5, width))) for n in lens]
+    refs = [plain_mixer(entry, x, w, dtype) for x in xs]
+    part = make_mixer(entry, dtype, w, width)
+    for plan in ([lens] + [[1, 1, 1]] * 5, [[140, 1, 3], [193, 129, 61]] + [[1, 1, 1]] * 5):
+        for g, ref in zip(run_mixer(part, dtype, xs, plan), refs):
+            assert close(g, ref, dtype)
+    saved = ops.RETENTION_CHUNKED_FROM
+    try:
+        ops.RETENTION_CHUNKED_FROM = 10 ** 9
+        chain = run_mixer(part, dtype, xs, [lens] + [[1, 1, 1]] * 5)
+    finally:
+        ops.RETENTION_CHUNKED_FROM = saved
+    for g, c, ref in zip(run_mixer(part, dtype, xs, [lens] + [[1, 1, 1]] * 5), chain, refs):
+        assert np.abs(g - c).max() <= FP32_TOL * np.abs(ref).max()
+
+
 LEFTS = [sh.left(), sh.left(heads=6, kv_heads=1, dim=8, dims=2, factor=0, scale=0.6, softcap=2.5),
          sh.left(heads=2, kv_heads=2, dim=64, dims=64, factor=8.0), sh.left(heads=3, kv_heads=3, dim=16, dims=None, softcap=0.0),
          sh.left(heads=2, kv_heads=1, dim=12, dims=4), sh.left(heads=1, kv_heads=1, dim=8, dims=8),
