@@ -585,9 +585,27 @@ extern "C" int qwb_delta_scan(const float* qkv, int ld, const float* kq, const f
 // a zero state (chunk_state), the carries through a sequence's chunks in order, which leave each chunk's S0 in the
 // scratch and the final state in the cache (chunk_carry), and the chunks' outputs (chunk_out).  A chunk is a block, so
 // a prompt of 2,048 tokens and 16 heads is 512 blocks instead of a chain of 2,048 steps.  The powers of d are made in
-// 64-bit.  qkv [T, ld]: q [H * K] | k [H * K] | v [H * P], already turned and scaled; scratch [B * chunks, H, P, K].
+// 64-bit.  qkv [T, ld]: q [H * K] | k [H * K] | v [H * P], already turned and scaled; scratch [2, B * chunks, H, P, K].
 // ---------------------------------------------------------------------------------
 #define QWB_CHUNK 64
+
+// 16 bytes from global to shared memory without a register in between: a block's loads are all in flight at once
+__device__ __forceinline__ void chunk_cp16(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void chunk_cp_wait() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// d^n for a small whole n, in 64-bit, by squaring (a dozen multiplications; the library's pow is a long routine)
+__device__ __forceinline__ double chunk_pow(double d, int n) {
+    double r = 1.0;
+    for (; n > 0; n >>= 1, d *= d)
+        if (n & 1) r *= d;
+    return r;
+}
 
 // grid (chunks, H, B), 256 threads; dynamic shared memory: QWB_CHUNK * (K + P + 1) floats
 __global__ void __launch_bounds__(256)
@@ -604,34 +622,48 @@ retention_chunk_state_kernel(const float* __restrict__ qkv, int ld, const float*
     float* vs = ks + QWB_CHUNK * K;         // [n][P], times d^(n - 1 - j)
     float* pw = vs + QWB_CHUNK * P;         // [QWB_CHUNK] powers of the decay
     const double d = (double)decay[h];
-    for (int i = threadIdx.x; i < QWB_CHUNK; i += blockDim.x) pw[i] = (float)pow(d, (double)i);
+    const int K4c = K >> 2, P4c = P >> 2;
+    for (int idx = threadIdx.x; idx < n * K4c; idx += blockDim.x) {
+        const int j = idx / K4c, k = (idx - j * K4c) * 4;
+        chunk_cp16(ks + j * K + k, qkv + (size_t)(t0 + j) * ld + (H + h) * K + k);
+    }
+    for (int idx = threadIdx.x; idx < n * P4c; idx += blockDim.x) {
+        const int j = idx / P4c, p = (idx - j * P4c) * 4;
+        chunk_cp16(vs + j * P + p, qkv + (size_t)(t0 + j) * ld + 2 * H * K + h * P + p);
+    }
+    for (int i = threadIdx.x; i < QWB_CHUNK; i += blockDim.x) pw[i] = (float)chunk_pow(d, i);
+    chunk_cp_wait();
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * K; idx += blockDim.x) {
-        const int j = idx / K, k = idx - j * K;
-        ks[idx] = qkv[(size_t)(t0 + j) * ld + (H + h) * K + k];
-    }
-    for (int idx = threadIdx.x; idx < n * P; idx += blockDim.x) {
-        const int j = idx / P, p = idx - j * P;
-        vs[idx] = qkv[(size_t)(t0 + j) * ld + 2 * H * K + h * P + p] * pw[n - 1 - j];
-    }
+    for (int idx = threadIdx.x; idx < n * P; idx += blockDim.x) vs[idx] *= pw[n - 1 - idx / P];
     __syncthreads();
     float* U = scratch + (((size_t)b * n_chunks + c) * H + h) * (size_t)P * K;
     const int K4 = K >> 2;
-    for (int idx = threadIdx.x; idx < P * K4; idx += blockDim.x) {
-        const int p = idx / K4, k4 = idx - p * K4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int j = 0; j < n; ++j) {
-            const float4 kk = *reinterpret_cast<const float4*>(ks + j * K + 4 * k4);
-            const float v = vs[j * P + p];
-            acc.x += kk.x * v; acc.y += kk.y * v; acc.z += kk.z * v; acc.w += kk.w * v;
+    {                                                               // 4 value columns x 4 key rows a thread
+        for (int idx = threadIdx.x; idx < (P >> 2) * K4; idx += blockDim.x) {
+            const int p4 = idx / K4, k4 = idx - p4 * K4;
+            float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
+#pragma unroll 4
+            for (int j = 0; j < n; ++j) {
+                const float4 kk = *reinterpret_cast<const float4*>(ks + j * K + 4 * k4);
+                const float4 vv = *reinterpret_cast<const float4*>(vs + j * P + 4 * p4);
+                a0.x += kk.x * vv.x; a0.y += kk.y * vv.x; a0.z += kk.z * vv.x; a0.w += kk.w * vv.x;
+                a1.x += kk.x * vv.y; a1.y += kk.y * vv.y; a1.z += kk.z * vv.y; a1.w += kk.w * vv.y;
+                a2.x += kk.x * vv.z; a2.y += kk.y * vv.z; a2.z += kk.z * vv.z; a2.w += kk.w * vv.z;
+                a3.x += kk.x * vv.w; a3.y += kk.y * vv.w; a3.z += kk.z * vv.w; a3.w += kk.w * vv.w;
+            }
+            float* u = U + (size_t)(4 * p4) * K + 4 * k4;
+            *reinterpret_cast<float4*>(u) = a0;
+            *reinterpret_cast<float4*>(u + K) = a1;
+            *reinterpret_cast<float4*>(u + 2 * K) = a2;
+            *reinterpret_cast<float4*>(u + 3 * K) = a3;
         }
-        *reinterpret_cast<float4*>(U + (size_t)p * K + 4 * k4) = acc;
     }
 }
 
 // grid (ceil(P * K / 256), H, B): every element of the state runs through its sequence's chunks in order
 __global__ void retention_chunk_carry_kernel(const float* __restrict__ decay, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
-                                             float* __restrict__ state, float* scratch, int H, int K, int P, int n_chunks, int write_state) {
+                                             float* __restrict__ state, const float* __restrict__ sums, float* __restrict__ starts,
+                                             int H, int K, int P, int n_chunks, int write_state) {
     pdl_wait();
     pdl_launch_dependents();
     const int e = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -639,16 +671,18 @@ __global__ void retention_chunk_carry_kernel(const float* __restrict__ decay, co
     const int n_tok = cu_seqlens[b + 1] - cu_seqlens[b];
     if (n_tok <= 0) return;
     const double d = (double)decay[h];
-    const float d_full = (float)pow(d, (double)QWB_CHUNK);
+    const float d_full = (float)chunk_pow(d, QWB_CHUNK);
     float* S = state + ((size_t)slots[b] * H + h) * (size_t)P * K + e;
     float s = *S;
     const int chunks = (n_tok + QWB_CHUNK - 1) / QWB_CHUNK;
+    const int last = n_tok - (chunks - 1) * QWB_CHUNK;
+    const float d_last = last == QWB_CHUNK ? d_full : (float)chunk_pow(d, last);
+    const size_t stride = (size_t)H * P * K, at = ((size_t)b * n_chunks * H + h) * (size_t)P * K + e;
+#pragma unroll 4
     for (int c = 0; c < chunks; ++c) {
-        float* U = scratch + (((size_t)b * n_chunks + c) * H + h) * (size_t)P * K + e;
-        const float own = *U;
-        *U = s;                                                     // the state this chunk starts from
-        const int n = min(QWB_CHUNK, n_tok - c * QWB_CHUNK);
-        s = (n == QWB_CHUNK ? d_full : (float)pow(d, (double)n)) * s + own;
+        const float own = sums[at + c * stride];
+        starts[at + c * stride] = s;                                // the state this chunk starts from
+        s = (c + 1 < chunks ? d_full : d_last) * s + own;
     }
     if (write_state) *S = s;
 }
@@ -666,30 +700,32 @@ retention_chunk_out_kernel(const float* __restrict__ qkv, int ld, const float* _
     if (t0 >= t1) return;
     const int n = t1 - t0, KP = K > P ? K : P;
     float* qs = co_smem;                    // [L][K]
-    float* kv = qs + L * K;                 // [L][max(K, P)]: the keys, then the values
-    float* A = kv + L * KP;                 // [L][L + 1]
-    float* S0 = A + L * (L + 1);            // [P][K + 1]
-    float* pw = S0 + (size_t)P * (K + 1);   // [L + 1] powers of the decay
+    float* kv = qs + L * K;                 // the keys [L][K + 4] (rows 16 bytes off a multiple of 128), then the values [L][P]
+    float* A = kv + L * (KP + 4);           // [L][L + 1]
+    float* S0 = A + L * (L + 1);            // [P][K + 4]: rows that start 16 bytes off a multiple of 128, read 16 bytes at a time
+    float* pw = S0 + (size_t)P * (K + 4);   // [L + 1] powers of the decay
     const double d = (double)decay[h];
-    for (int i = threadIdx.x; i <= L; i += blockDim.x) pw[i] = (float)pow(d, (double)i);
-    for (int idx = threadIdx.x; idx < n * K; idx += blockDim.x) {
-        const int j = idx / K, k = idx - j * K;
+    const int K4c = K >> 2, P4c = P >> 2;
+    for (int idx = threadIdx.x; idx < n * K4c; idx += blockDim.x) {
+        const int j = idx / K4c, k = (idx - j * K4c) * 4;
         const float* row = qkv + (size_t)(t0 + j) * ld;
-        qs[j * K + k] = row[h * K + k];
-        kv[j * K + k] = row[(H + h) * K + k];
+        chunk_cp16(qs + j * K + k, row + h * K + k);
+        chunk_cp16(kv + j * (K + 4) + k, row + (H + h) * K + k);
     }
     const float* S = scratch + (((size_t)b * n_chunks + c) * H + h) * (size_t)P * K;
-    for (int idx = threadIdx.x; idx < P * K; idx += blockDim.x) {
-        const int p = idx / K, k = idx - p * K;
-        S0[p * (K + 1) + k] = S[idx];
+    for (int idx = threadIdx.x; idx < P * K4c; idx += blockDim.x) {
+        const int p = idx / K4c, k = (idx - p * K4c) * 4;
+        chunk_cp16(S0 + p * (K + 4) + k, S + (size_t)p * K + k);
     }
+    for (int i = threadIdx.x; i <= L; i += blockDim.x) pw[i] = (float)chunk_pow(d, i);
+    chunk_cp_wait();
     __syncthreads();
     for (int idx = threadIdx.x; idx < n * n; idx += blockDim.x) {      // A[i][j] = d^(i - j) q_i . k_j for j <= i
         const int i = idx / n, j = idx - i * n;
         float dot = 0.f;
         if (j <= i) {
             const float4* qa = reinterpret_cast<const float4*>(qs + i * K);
-            const float4* kb = reinterpret_cast<const float4*>(kv + j * K);
+            const float4* kb = reinterpret_cast<const float4*>(kv + j * (K + 4));
             for (int k = 0; k < (K >> 2); ++k) {
                 const float4 x = qa[k], y = kb[k];
                 dot += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
@@ -699,10 +735,11 @@ retention_chunk_out_kernel(const float* __restrict__ qkv, int ld, const float* _
         A[i * (L + 1) + j] = dot;
     }
     __syncthreads();                                                    // the keys are no longer read
-    for (int idx = threadIdx.x; idx < n * P; idx += blockDim.x) {
-        const int j = idx / P, p = idx - j * P;
-        kv[j * P + p] = qkv[(size_t)(t0 + j) * ld + 2 * H * K + h * P + p];
+    for (int idx = threadIdx.x; idx < n * P4c; idx += blockDim.x) {
+        const int j = idx / P4c, p = (idx - j * P4c) * 4;
+        chunk_cp16(kv + j * P + p, qkv + (size_t)(t0 + j) * ld + 2 * H * K + h * P + p);
     }
+    chunk_cp_wait();
     __syncthreads();
     const int groups = (n + IB - 1) / IB;
     for (int idx = threadIdx.x; idx < groups * P; idx += blockDim.x) {  // IB tokens of one value column a thread
@@ -710,11 +747,17 @@ retention_chunk_out_kernel(const float* __restrict__ qkv, int ld, const float* _
         float acc[IB];
 #pragma unroll
         for (int ii = 0; ii < IB; ++ii) acc[ii] = 0.f;
-        const float* srow = S0 + p * (K + 1);
-        for (int k = 0; k < K; ++k) {
-            const float sv = srow[k];
+        const float4* srow = reinterpret_cast<const float4*>(S0 + p * (K + 4));
+        const float4* qrow[IB];
 #pragma unroll
-            for (int ii = 0; ii < IB; ++ii) acc[ii] += sv * qs[min(i0 + ii, n - 1) * K + k];
+        for (int ii = 0; ii < IB; ++ii) qrow[ii] = reinterpret_cast<const float4*>(qs + min(i0 + ii, n - 1) * K);
+        for (int k = 0; k < (K >> 2); ++k) {
+            const float4 sv = srow[k];
+#pragma unroll
+            for (int ii = 0; ii < IB; ++ii) {
+                const float4 qv = qrow[ii][k];
+                acc[ii] += sv.x * qv.x + sv.y * qv.y + sv.z * qv.z + sv.w * qv.w;
+            }
         }
 #pragma unroll
         for (int ii = 0; ii < IB; ++ii) acc[ii] *= pw[min(i0 + ii, n - 1) + 1];
@@ -732,17 +775,17 @@ retention_chunk_out_kernel(const float* __restrict__ qkv, int ld, const float* _
 
 static size_t retention_chunk_smem_floats(int K, int P) {
     const int KP = K > P ? K : P;
-    return (size_t)QWB_CHUNK * K + (size_t)QWB_CHUNK * KP + (size_t)QWB_CHUNK * (QWB_CHUNK + 1) + (size_t)P * (K + 1) + QWB_CHUNK + 1;
+    return (size_t)QWB_CHUNK * K + (size_t)QWB_CHUNK * (KP + 4) + (size_t)QWB_CHUNK * (QWB_CHUNK + 1) + (size_t)P * (K + 4) + QWB_CHUNK + 1;
 }
 
-// 1 if the chunked form takes these sizes (keys in multiples of 4, tiles that fit in shared memory)
+// 1 if the chunked form takes these sizes (keys and values in multiples of 4, tiles that fit in shared memory)
 extern "C" int qwb_retention_chunked_fits(int K, int P) {
-    return K > 0 && P > 0 && K % 4 == 0 && retention_chunk_smem_floats(K, P) * sizeof(float) <= 200 * 1024;
+    return K > 0 && P > 0 && K % 4 == 0 && P % 4 == 0 && retention_chunk_smem_floats(K, P) * sizeof(float) <= 200 * 1024;
 }
 
 extern "C" int qwb_retention_chunk_len() { return QWB_CHUNK; }
 
-// scratch: B * ceil(max_new / 64) * H * P * K floats
+// scratch: 2 * B * ceil(max_new / 64) * H * P * K floats (the chunks' own sums, then the states they start from)
 extern "C" int qwb_retention_chunked(const float* qkv, int ld, const float* decay, float* state, const int* cu_seqlens, const int* slots,
                                      float* scratch, float* o, int B, int max_new, int H, int K, int P, int write_state, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
@@ -757,9 +800,10 @@ extern "C" int qwb_retention_chunked(const float* qkv, int ld, const float* deca
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "retention_chunked: %s", cudaGetErrorString(e));
     qwb_launch(retention_chunk_state_kernel, dim3(n_chunks, H, B), 256, smem1, stream, qkv, ld, decay, cu_seqlens, scratch, H, K, P, n_chunks);
     if (int rc = qwb_check_launch("retention_chunk_state")) return rc;
-    qwb_launch(retention_chunk_carry_kernel, dim3((P * K + 255) / 256, H, B), 256, 0, stream, decay, cu_seqlens, slots, state, scratch, H, K, P, n_chunks, write_state);
+    float* starts = scratch + (size_t)B * n_chunks * H * P * K;
+    qwb_launch(retention_chunk_carry_kernel, dim3((P * K + 255) / 256, H, B), 256, 0, stream, decay, cu_seqlens, slots, state, (const float*)scratch, starts, H, K, P, n_chunks, write_state);
     if (int rc = qwb_check_launch("retention_chunk_carry")) return rc;
-    qwb_launch(retention_chunk_out_kernel, dim3(n_chunks, H, B), 256, smem3, stream, qkv, ld, decay, cu_seqlens, (const float*)scratch, o, H, K, P, n_chunks);
+    qwb_launch(retention_chunk_out_kernel, dim3(n_chunks, H, B), 256, smem3, stream, qkv, ld, decay, cu_seqlens, (const float*)starts, o, H, K, P, n_chunks);
     return qwb_check_launch("retention_chunk_out");
 }
 

@@ -951,7 +951,7 @@ def retention_scan(qkv: torch.Tensor, cos, sin, rotary_dim: int, decay: torch.Te
     if chunked and qkv.shape[1] % 4 == 0 and retention_chunked_fits(key_dim, vdim):
         # long prompts: chunks of 64 tokens side by side (three kernels) instead of a chain through every token
         n_chunks = -(-ctx.max_new // RETENTION_CHUNK)
-        scratch = torch.empty((ctx.n_seqs * n_chunks, heads, vdim, key_dim), dtype=torch.float32, device=dev)
+        scratch = torch.empty((2, ctx.n_seqs * n_chunks, heads, vdim, key_dim), dtype=torch.float32, device=dev)
         _call("recurrent", "qwb_retention_chunked", _ptr(qkv), _i(qkv.shape[1]), _ptr(decay), _ptr(state), _ptr(ctx.cu_seqlens),
               _ptr(ctx.slots), _ptr(scratch), _ptr(o), _i(ctx.n_seqs), _i(ctx.max_new), _i(heads), _i(key_dim), _i(vdim),
               _i(1 if write_state else 0), _stream(), kernels=3)
