@@ -20,6 +20,7 @@
 //   bias_decode    one new token per sequence: runs of pages, one block of threads a run, then bias_merge, which also adds
 //                  the sink
 //   bias_head_mix  the mix of the heads and the gate
+//   bias_decode_mixed  one new token per sequence with mixed heads, in two passes over the keys
 #include "common.cuh"
 
 #define QWB_BIAS_MAX_DIM 256
@@ -594,7 +595,7 @@ __global__ void bias_decode_kernel(const T* __restrict__ q, const T* __restrict_
                                    const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
                                    float* __restrict__ part_m, float* __restrict__ part_l, int H, int G, int C, int dim, int vdim,
                                    int table_width, float scale, const float* __restrict__ head_scale, float softcap,
-                                   const float* __restrict__ slopes, int window, int n_runs) {
+                                   const float* __restrict__ slopes, int window, int n_runs, int stats_only) {
     pdl_wait();
     pdl_launch_dependents();
     constexpr int RT = QWB_BIAS_ROWS, VEC = Vec16<T>::N, PG = QWB_BIAS_PAGE;
@@ -656,7 +657,8 @@ __global__ void bias_decode_kernel(const T* __restrict__ q, const T* __restrict_
             uint4* vdst = reinterpret_cast<uint4*>(Vt);
             for (int i = tid; i < n_keys * dchunk; i += blockDim.x) bias_cp16(kdst + i + i / dchunk, ksrc + i);     // row r starts at r * (dchunk + 1)
             asm volatile("cp.async.commit_group;" ::: "memory");
-            for (int i = tid; i < n_keys * vdim / VEC; i += blockDim.x) bias_cp16(vdst + i, vsrc + i);
+            if (!stats_only)
+                for (int i = tid; i < n_keys * vdim / VEC; i += blockDim.x) bias_cp16(vdst + i, vsrc + i);
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 1;" ::: "memory");     // the keys are there; the values arrive under the scores
         }
@@ -712,6 +714,7 @@ __global__ void bias_decode_kernel(const T* __restrict__ q, const T* __restrict_
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
+        if (stats_only) continue;                                     // maxima and sums only: the values are not read
 
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
@@ -743,7 +746,7 @@ __global__ void bias_decode_kernel(const T* __restrict__ q, const T* __restrict_
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
         const int d = tid + cc * 128;
-        if (d >= vdim) continue;
+        if (d >= vdim || stats_only) continue;
 #pragma unroll
         for (int ri = 0; ri < RT; ++ri)
             if (ri < rcount) part_acc[((((size_t)b * H + head0 + ri) * C + c) * n_runs + run) * vdim + d] = acc[ri][cc];
@@ -832,7 +835,7 @@ static int launch_bias_decode(const void* q, const void* k_pool, const void* v_p
     const int slices = (H / G + QWB_BIAS_ROWS - 1) / QWB_BIAS_ROWS;
     qwb_launch(bias_decode_kernel<T>, dim3(n_runs, G * slices * C, B), 128, smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool,
                page_table, seq_len, part_acc, part_m, part_l, H, G, C, dim, vdim, table_width, scale, head_scale, softcap, slopes, window,
-               n_runs);
+               n_runs, 0);
     if (int rc = qwb_check_launch("bias_decode")) return rc;
     qwb_launch(bias_merge_kernel<TO>, dim3(H * C, B), 128, 0, stream, (const float*)part_acc, (const float*)part_m, (const float*)part_l,
                seq_len, (TO*)out, C, vdim, window, n_runs, sinks);
@@ -855,6 +858,293 @@ extern "C" int qwb_bias_decode(const void* q, const void* k_pool, const void* v_
     if (dtype == QWB_DT_BF16) return raw_out ? QWB_BIAS_DEC(bf16, float) : QWB_BIAS_DEC(bf16, bf16);
 #undef QWB_BIAS_DEC
     return qwb_fail(QWB_ERR_ARG, "bias_decode: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------
+// decode with mixed heads in two passes over the keys.  The mix needs every head's NORMALISED weights, so the first
+// pass (the decode kernel above without its values) leaves each run's maxima and sums, bias_stats_kernel turns them
+// into each head's maximum M and 1 / denominator (with the sink), and the second pass, one block per (run, sequence) for
+// ALL heads, forms for a page of keys every head's weights e^(s - M) / L in shared memory, mixes them there,
+// w'_h = sum_g mix[h, g] w_g, and adds w'_h times the values of h's own value head onto its sums: keys twice and values
+// once, where the form with all value heads reads the keys and forms the scores once per value head.  The runs' sums
+// simply add up (the weights are final), which bias_mixed_merge does, with the gate.
+// ---------------------------------------------------------------------------------
+#define QWB_BIAS_MIXED_THREADS 256
+#define QWB_BIAS_MIXED_ACC 16      // sums a thread keeps: H * vdim <= 256 * 16
+
+// grid (H, B), 32 threads: stats [B, H, 2] = the maximum (of the runs and the sink) and 1 / denominator
+__global__ void bias_stats_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l, const int* __restrict__ seq_len,
+                                  float* __restrict__ stats, int window, int n_runs, const float* __restrict__ sinks) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+    const size_t row = (size_t)b * gridDim.x + h;
+    const int len = seq_len[b];
+    const int first = bias_first_key(len - 1, window);
+    const int rp = bias_run_pages(first, len);
+    const int runs = min(n_runs, ((len - 1) / QWB_BIAS_PAGE - first / QWB_BIAS_PAGE) / rp + 1);
+    float M = sinks ? sinks[h] : -INFINITY;
+    for (int r = lane; r < runs; r += 32) M = fmaxf(M, part_m[row * n_runs + r]);
+    M = warp_max(M);
+    float L = 0.f;
+    for (int r = lane; r < runs; r += 32) L += part_l[row * n_runs + r] * (M == -INFINITY ? 0.f : expf(part_m[row * n_runs + r] - M));
+    L = warp_sum(L);
+    if (sinks) L += expf(sinks[h] - M);
+    if (lane == 0) { stats[2 * row] = M; stats[2 * row + 1] = L > 0.f ? 1.f / L : 0.f; }
+}
+
+__device__ __forceinline__ void bias_load2(const float* p, float& a, float& b) { const float2 v = *reinterpret_cast<const float2*>(p); a = v.x; b = v.y; }
+__device__ __forceinline__ void bias_load2(const bf16* p, float& a, float& b) {
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+    a = __uint_as_float(v << 16); b = __uint_as_float(v & 0xffff0000u);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QWB_BIAS_MIXED_THREADS)
+bias_decode_mixed_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                         const int* __restrict__ page_table, const int* __restrict__ seq_len, const float* __restrict__ stats,
+                         const float* __restrict__ mix, float* __restrict__ part, int H, int G, int dim, int vdim, int table_width,
+                         float scale, const float* __restrict__ head_scale, float softcap, const float* __restrict__ slopes, int window,
+                         int n_runs) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int VEC = Vec16<T>::N, PG = QWB_BIAS_PAGE, NT = QWB_BIAS_MIXED_THREADS, NA = QWB_BIAS_MIXED_ACC, RT = QWB_BIAS_ROWS;
+    const int b = blockIdx.y, run = blockIdx.x;
+    const int len = seq_len[b];
+    const int first = bias_first_key(len - 1, window);
+    const int rp = bias_run_pages(first, len);
+    const int page_lo = first / PG;
+    const int row_first = max(first, (page_lo + run * rp) * PG);
+    const int row_end = min(len, (page_lo + (run + 1) * rp) * PG);
+    float* out = part + ((size_t)b * n_runs + run) * H * vdim;
+    const int tid = threadIdx.x;
+    if (row_first >= row_end) {                                      // a run without keys adds nothing
+        for (int i = tid; i < H * vdim; i += NT) out[i] = 0.f;
+        return;
+    }
+    const int QG = H / G;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int kld = dim + VEC;
+    const size_t tile_elems = (size_t)G * PG * (kld > vdim ? kld : vdim);
+    T* tile = reinterpret_cast<T*>(smem_raw);                        // the keys of all key heads [G][PG][dim + VEC], then the values [G][PG][vdim]
+    float* qs = reinterpret_cast<float*>(tile + tile_elems);         // [H][dim], scaled
+    float* w = qs + (size_t)H * dim;                                 // [H][PG] normalised weights
+    float* w2 = w + (size_t)H * PG;                                  // [H][PG] mixed
+    float* mx = w2 + (size_t)H * PG;                                 // [H][H]
+    float* st = mx + (size_t)H * H;                                  // [H][3]: maximum, 1 / denominator, slope
+
+    for (int idx = tid; idx < H * dim; idx += NT) {
+        const int h = idx / dim;
+        qs[idx] = to_f32(q[(size_t)b * H * dim + idx]) * scale * (head_scale ? head_scale[h] : 1.f);
+    }
+    for (int idx = tid; idx < H * H; idx += NT) mx[idx] = mix[idx];
+    for (int h = tid; h < H; h += NT) {
+        st[3 * h] = stats[2 * ((size_t)b * H + h)];
+        st[3 * h + 1] = stats[2 * ((size_t)b * H + h) + 1];
+        st[3 * h + 2] = slopes ? slopes[h] : 0.f;
+    }
+    float acc[NA];
+#pragma unroll
+    for (int i = 0; i < NA; ++i) acc[i] = 0.f;
+
+    const int* pages = page_table + (size_t)b * table_width;
+    const int dchunk = dim / VEC;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+
+    for (int base = (row_first / PG) * PG; base < row_end; base += PG) {
+        const int n_keys = min(PG, row_end - base);
+        const size_t page = (size_t)pages[base / PG];
+        __syncthreads();                                              // the last page's values are no longer read
+        for (int i = tid; i < G * n_keys * dchunk; i += NT) {
+            const int g = i / (n_keys * dchunk), rest = i - g * n_keys * dchunk, r = rest / dchunk, ch = rest - r * dchunk;
+            bias_cp16(tile + ((size_t)g * PG + r) * kld + ch * VEC, k_pool + ((page * G + g) * PG + r) * (size_t)dim + ch * VEC);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        // every head's weights for the page's keys: a thread takes a key of a key head and up to 8 of its query heads at a time
+        for (int item = tid; item < G * PG; item += NT) {
+            const int g = item / PG, key = item - g * PG;
+            const bool ok = key < n_keys && base + key >= row_first;
+            const float dist = (float)(len - 1 - (base + key));
+            const Vec16<T>* krow = reinterpret_cast<const Vec16<T>*>(tile + ((size_t)g * PG + key) * kld);
+            for (int h0 = 0; h0 < QG; h0 += RT) {
+                float s[RT];
+#pragma unroll
+                for (int k = 0; k < RT; ++k) s[k] = 0.f;
+                if (ok) {
+                    for (int ch = 0; ch < dchunk; ++ch) {
+                        float kf[VEC];
+                        krow[ch].get(kf);
+#pragma unroll
+                        for (int k = 0; k < RT; ++k) {
+                            if (h0 + k < QG) {
+                                const float4* qr = reinterpret_cast<const float4*>(qs + (size_t)(g * QG + h0 + k) * dim + ch * VEC);
+#pragma unroll
+                                for (int e = 0; e < VEC / 4; ++e) {
+                                    const float4 qv = qr[e];
+                                    s[k] += qv.x * kf[4 * e] + qv.y * kf[4 * e + 1] + qv.z * kf[4 * e + 2] + qv.w * kf[4 * e + 3];
+                                }
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < RT; ++k) {
+                    if (h0 + k < QG) {
+                        const int h = g * QG + h0 + k;
+                        w[h * PG + key] = ok ? expf(bias_cap(s[k], softcap, inv_cap) - st[3 * h + 2] * dist - st[3 * h]) * st[3 * h + 1] : 0.f;
+                    }
+                }
+            }
+        }
+        __syncthreads();                                              // the keys are no longer read: the values may come
+        for (int i = tid; i < G * n_keys * (vdim / VEC); i += NT) {
+            const int per = n_keys * (vdim / VEC), g = i / per, rest = i - g * per;
+            bias_cp16(tile + (size_t)g * PG * vdim + (size_t)rest * VEC, v_pool + (page * G + g) * PG * (size_t)vdim + (size_t)rest * VEC);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        for (int idx = tid; idx < H * PG; idx += NT) {                // the mix, under the values' copy
+            const int h = idx / PG, key = idx - h * PG;
+            float v = 0.f;
+            for (int g2 = 0; g2 < H; ++g2) v += mx[h * H + g2] * w[g2 * PG + key];
+            w2[idx] = v;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        // a thread keeps pairs of neighbouring value columns: four keys' weights in one load, two values in one
+        const int half = vdim >> 1;
+#pragma unroll
+        for (int i = 0; i < NA / 2; ++i) {
+            const int idx = tid + i * NT;
+            if (idx < H * half) {
+                const int h = idx / half, d = (idx - h * half) * 2;
+                const T* vcol = tile + (size_t)(h / QG) * PG * vdim + d;
+                const float* wr = w2 + h * PG;
+                float a0 = acc[2 * i], a1 = acc[2 * i + 1];
+                int j = 0;
+                for (; j + 4 <= n_keys; j += 4) {
+                    const float4 p = *reinterpret_cast<const float4*>(wr + j);
+                    float x0, y0, x1, y1, x2, y2, x3, y3;
+                    bias_load2(vcol + (size_t)j * vdim, x0, y0);
+                    bias_load2(vcol + (size_t)(j + 1) * vdim, x1, y1);
+                    bias_load2(vcol + (size_t)(j + 2) * vdim, x2, y2);
+                    bias_load2(vcol + (size_t)(j + 3) * vdim, x3, y3);
+                    a0 += p.x * x0 + p.y * x1 + p.z * x2 + p.w * x3;
+                    a1 += p.x * y0 + p.y * y1 + p.z * y2 + p.w * y3;
+                }
+                for (; j < n_keys; ++j) {
+                    float x, y;
+                    bias_load2(vcol + (size_t)j * vdim, x, y);
+                    a0 += wr[j] * x; a1 += wr[j] * y;
+                }
+                acc[2 * i] = a0; acc[2 * i + 1] = a1;
+            }
+        }
+    }
+    const int half = vdim >> 1;
+#pragma unroll
+    for (int i = 0; i < NA / 2; ++i) {
+        const int idx = tid + i * NT;
+        if (idx < H * half) {
+            const int h = idx / half, d = (idx - h * half) * 2;
+            out[h * vdim + d] = acc[2 * i];
+            out[h * vdim + d + 1] = acc[2 * i + 1];
+        }
+    }
+}
+
+// out[b, h, :] = sigmoid(gate[b, h]) * sum over the sequence's runs, in index order; grid (H, B)
+template <typename TO>
+__global__ void bias_mixed_merge_kernel(const float* __restrict__ part, const int* __restrict__ seq_len, const float* __restrict__ gate,
+                                        int ld_gate, TO* __restrict__ out, int H, int vdim, int window, int n_runs) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int len = seq_len[b];
+    const int first = bias_first_key(len - 1, window);
+    const int rp = bias_run_pages(first, len);
+    const int runs = min(n_runs, ((len - 1) / QWB_BIAS_PAGE - first / QWB_BIAS_PAGE) / rp + 1);
+    const float gt = gate ? 1.f / (1.f + expf(-gate[(size_t)b * ld_gate + h])) : 1.f;
+    for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+        float a = 0.f;
+        for (int r = 0; r < runs; ++r) a += part[(((size_t)b * n_runs + r) * H + h) * vdim + d];
+        out[((size_t)b * H + h) * vdim + d] = from_f32<TO>(a * gt);
+    }
+}
+
+template <typename T>
+static size_t bias_mixed_smem(int H, int G, int dim, int vdim) {
+    constexpr int VEC = Vec16<T>::N;
+    const int kld = dim + VEC;
+    return (size_t)G * QWB_BIAS_PAGE * (kld > vdim ? kld : vdim) * sizeof(T) +
+           ((size_t)H * dim + 2 * (size_t)H * QWB_BIAS_PAGE + (size_t)H * H + 3 * (size_t)H) * sizeof(float);
+}
+
+// 1 if the two-pass form takes these sizes
+extern "C" int qwb_bias_decode_mixed_fits(int dtype, int H, int G, int dim, int vdim) {
+    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || dim % 8 || vdim % 8 || dim > QWB_BIAS_MAX_DIM || vdim > QWB_BIAS_MAX_DIM) return 0;
+    if ((long long)H * vdim > (long long)QWB_BIAS_MIXED_THREADS * QWB_BIAS_MIXED_ACC) return 0;
+    const size_t smem = dtype == QWB_DT_F32 ? bias_mixed_smem<float>(H, G, dim, vdim) : bias_mixed_smem<bf16>(H, G, dim, vdim);
+    return (dtype == QWB_DT_F32 || dtype == QWB_DT_BF16) && smem <= 200 * 1024;
+}
+
+// floats of scratch: the first pass's maxima and sums, the heads' stats, the runs' sums
+extern "C" long long qwb_bias_decode_mixed_scratch_floats(int B, int H, int vdim, int n_runs) {
+    return (long long)B * H * (2 * n_runs + 2) + (long long)B * n_runs * H * vdim;
+}
+
+template <typename T>
+static int launch_bias_decode_mixed(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
+                                    float* scratch, void* out, int B, int H, int G, int dim, int vdim, int table_width, float scale,
+                                    const float* head_scale, float softcap, const float* slopes, int window, const float* sinks,
+                                    const float* mix, const float* gate, int ld_gate, int n_runs, cudaStream_t stream) {
+    constexpr int VEC = Vec16<T>::N;
+    float* part_m = scratch;
+    float* part_l = part_m + (size_t)B * H * n_runs;
+    float* stats = part_l + (size_t)B * H * n_runs;
+    float* part = stats + (size_t)B * H * 2;
+    const size_t smem1 = ((size_t)QWB_BIAS_PAGE * (dim + VEC) + (size_t)QWB_BIAS_PAGE * vdim) * sizeof(T) +
+                         ((size_t)QWB_BIAS_ROWS * dim + QWB_BIAS_ROWS * QWB_BIAS_PAGE + 4 * QWB_BIAS_ROWS) * sizeof(float);
+    const size_t smem2 = bias_mixed_smem<T>(H, G, dim, vdim);
+    cudaError_t e = cudaSuccess;
+    if (smem1 > 48 * 1024) e = cudaFuncSetAttribute(bias_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (e == cudaSuccess && smem2 > 48 * 1024) e = cudaFuncSetAttribute(bias_decode_mixed_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "bias_decode_mixed: %s", cudaGetErrorString(e));
+    const int slices = (H / G + QWB_BIAS_ROWS - 1) / QWB_BIAS_ROWS;
+    qwb_launch(bias_decode_kernel<T>, dim3(n_runs, G * slices, B), 128, smem1, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool,
+               page_table, seq_len, (float*)nullptr, part_m, part_l, H, G, 1, dim, vdim, table_width, scale, head_scale, softcap, slopes,
+               window, n_runs, 1);
+    if (int rc = qwb_check_launch("bias_decode (maxima and sums)")) return rc;
+    qwb_launch(bias_stats_kernel, dim3(H, B), 32, 0, stream, (const float*)part_m, (const float*)part_l, seq_len, stats, window, n_runs, sinks);
+    if (int rc = qwb_check_launch("bias_stats")) return rc;
+    qwb_launch(bias_decode_mixed_kernel<T>, dim3(n_runs, B), QWB_BIAS_MIXED_THREADS, smem2, stream, (const T*)q, (const T*)k_pool,
+               (const T*)v_pool, page_table, seq_len, (const float*)stats, mix, part, H, G, dim, vdim, table_width, scale, head_scale,
+               softcap, slopes, window, n_runs);
+    if (int rc = qwb_check_launch("bias_decode_mixed")) return rc;
+    const int block = vdim >= 128 ? 128 : (vdim >= 64 ? 64 : 32);
+    qwb_launch(bias_mixed_merge_kernel<T>, dim3(H, B), block, 0, stream, (const float*)part, seq_len, gate, ld_gate, (T*)out, H, vdim,
+               window, n_runs);
+    return qwb_check_launch("bias_mixed_merge");
+}
+
+// q [B, H, dim]; out [B, H * vdim] in the cache's dtype; mix [H, H]; gate: H columns of a float matrix with rows of ld_gate
+// values, or null; scratch: qwb_bias_decode_mixed_scratch_floats floats.
+extern "C" int qwb_bias_decode_mixed(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
+                                     float* scratch, void* out, int dtype, int B, int H, int G, int dim, int vdim, int table_width,
+                                     float scale, const float* head_scale, float softcap, const float* slopes, int window,
+                                     const float* sinks, const float* mix, const float* gate, int ld_gate, int n_runs,
+                                     cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (int rc = check_bias_sizes("bias_decode_mixed", H, G, dim, vdim, table_width, window, 8)) return rc;
+    if (!mix || !qwb_bias_decode_mixed_fits(dtype, H, G, dim, vdim))
+        return qwb_fail(QWB_ERR_ARG, "bias_decode_mixed: %d heads over %d, keys of %d and values of %d do not fit this form", H, G, dim, vdim);
+    if (n_runs <= 0 || n_runs > 65535 || B > 65535) return qwb_fail(QWB_ERR_ARG, "bias_decode_mixed: %d runs, %d sequences", n_runs, B);
+    if (dtype == QWB_DT_F32)
+        return launch_bias_decode_mixed<float>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, H, G, dim, vdim, table_width, scale,
+                                               head_scale, softcap, slopes, window, sinks, mix, gate, ld_gate, n_runs, stream);
+    return launch_bias_decode_mixed<bf16>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, H, G, dim, vdim, table_width, scale,
+                                          head_scale, softcap, slopes, window, sinks, mix, gate, ld_gate, n_runs, stream);
 }
 
 // ---------------------------------------------------------------------------------

@@ -1260,6 +1260,10 @@ BIAS_ATTN_MAX_DIM = 256     # csrc/attention_bias.cu: QWB_BIAS_MAX_DIM
 BIAS_ATTN_FAST_STEP = 8     # key and value sizes that are multiples of this take the kernels that copy 16 bytes at a time
 BIAS_PREFILL_MMA = True     # bfloat16 prompts take the tensor-core kernel where it fits; False: always the plain one
 BIAS_MMA_MIN_NEW = 16       # ... from this many new tokens of the longest sequence on (a tile is 64 queries)
+BIAS_DECODE_TWO_PASS = True # single tokens with mixed heads take the two-pass kernels where they fit (False: all value heads) ...
+BIAS_TWO_PASS_FROM_KEYS = 24576     # ... from this many keys in the step (sequences x the bound on their lengths): below, the
+                                    # form with all value heads has 16 times the blocks and one kernel less, and is faster
+                                    # (8 sequences of 1,024 tokens: 0.495 against 0.515 ms a step; one: 0.391 against 0.460)
 
 
 def bias_prefill_mma_fits(dtype: torch.dtype, dim: int, vdim: int) -> bool:
@@ -1334,6 +1338,23 @@ def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: floa
         _need(gate, "gate", torch.float32, 2)
         if gate.shape[0] != T or gate_col0 < 0 or gate_col0 + H > gate.shape[1]:
             raise KernelError(f"bias_attention: gate {tuple(gate.shape)} from column {gate_col0} for {T} tokens of {H} heads")
+    width = page_table.shape[1]
+    if (head_mix is not None and ctx.single_token and BIAS_DECODE_TWO_PASS and T * ctx.max_len >= BIAS_TWO_PASS_FROM_KEYS
+            and _lookup("attention_bias", "qwb_bias_decode_mixed_fits")[1](_i(_dt(q.dtype)), _i(H), _i(G), _i(dim), _i(vdim))):
+        # mixed heads, one token per sequence: every head's maximum and sum first, then all heads' final weights mixed in
+        # shared memory and applied to their own value heads (keys twice, values once)
+        lib = _lookup("attention_bias", "qwb_bias_decode_runs")[0]
+        n_runs = lib.qwb_bias_decode_runs(_i(ctx.max_len), _i(window))
+        lib.qwb_bias_decode_mixed_scratch_floats.restype = ctypes.c_longlong
+        scratch = torch.empty((lib.qwb_bias_decode_mixed_scratch_floats(_i(T), _i(H), _i(vdim), _i(n_runs)),),
+                              dtype=torch.float32, device=q.device)
+        out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
+        _call("attention_bias", "qwb_bias_decode_mixed", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.seq_len),
+              _ptr(scratch), _ptr(out), _i(_dt(q.dtype)), _i(T), _i(H), _i(G), _i(dim), _i(vdim), _i(width), _f(scale),
+              _ptr(head_scale), _f(softcap), _ptr(slopes), _i(window), _ptr(sinks), _ptr(head_mix),
+              ctypes.c_void_p(gate.data_ptr() + 4 * gate_col0) if gate is not None else _ptr(None),
+              _i(gate.shape[1] if gate is not None else 0), _i(n_runs), _stream(), kernels=4)
+        return out
     all_values = head_mix is not None
     raw = all_values or gate is not None
     C = G if all_values else 1

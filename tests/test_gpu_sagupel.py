@@ -420,6 +420,9 @@ def test_the_sink_takes_its_share():
 
 
 # ----------------------------------------------------------------------------- the prompt kernel on the tensor cores
+TWO_PASS_FROM = ops.BIAS_TWO_PASS_FROM_KEYS
+
+
 def shaped_oracle(q, k, v, pos0, scale, head_scale, softcap, slopes, window, sinks, mix, gate):
     """q [n, H, dim], k [L, G, dim], v [L, G, vdim] of one sequence (float64); the n queries sit at pos0 .. pos0 + n - 1.
     Returns [n, H * vdim]."""
@@ -485,8 +488,11 @@ def test_prompt_kernels_and_the_decode_kernel_against_an_oracle(H, G, dim, vdim,
                                                  None if gates is None else gates[b])
                                    for b, (q, k, v, n0) in enumerate(zip(qs, ks, vs, before))])
             gate = None if gates is None else dev(np.concatenate([np.zeros((sum(counts), 3)), np.concatenate(gates)], axis=1))
-            impls = ["auto"] if ctx.single_token else (["plain", "mma"] if dtype == torch.bfloat16 and dim % 16 == 0 else ["plain"])
+            impls = ["auto", "two_pass"] if ctx.single_token else (["plain", "mma"] if dtype == torch.bfloat16 and dim % 16 == 0 else ["plain"])
             for impl in impls:
+                # single tokens with mixed heads: the form with all value heads, and the two passes over the keys
+                ops.BIAS_TWO_PASS_FROM_KEYS = 0 if impl == "two_pass" else 10 ** 9
+                impl = "auto" if impl == "two_pass" else impl
                 got = ops.bias_attention(dev(np.concatenate(qs), dtype), unit.k_pool, unit.v_pool, ctx.page_tables[unit.group_id], ctx, 0.3,
                                          head_scale=None if head_scale is None else dev(head_scale), softcap=softcap,
                                          slopes=None if slopes is None else dev(slopes), window=window,
@@ -495,6 +501,7 @@ def test_prompt_kernels_and_the_decode_kernel_against_an_oracle(H, G, dim, vdim,
                 tol = 1e-4 if dtype == torch.float32 else 0.02
                 assert np.abs(got - want).max() <= tol * max(np.abs(want).max(), 1.0), (dtype, counts, impl)
             cache.close(slots)
+    ops.BIAS_TWO_PASS_FROM_KEYS = TWO_PASS_FROM
 
 
 # ----------------------------------------------------------------------------- whole models
