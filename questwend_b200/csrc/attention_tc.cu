@@ -123,12 +123,13 @@ struct AtSmem {
     static constexpr size_t BYTES = Q_BYTES + 2 * AT_KV_STAGES * KV_BYTES + P_BYTES + 128;   // 128: barriers, tensor-memory slot
 };
 
-template <int HD>
+template <int HD, bool SHAPED>      // SHAPED: the softmax also takes a distance bias per head and a sink (else the kernel is as it was)
 __global__ void __launch_bounds__(AT_THREADS)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ pos0, bf16* __restrict__ out, int Hq, int Hkv,
-                       int table_width, float scale, int window, int chunk, int G, int* error) {
+                       int table_width, float scale, int window, int chunk, int G, int* error,
+                       const float* __restrict__ slopes, const float* __restrict__ sinks) {
     constexpr int ATOMS = AtSmem<HD>::ATOMS;
     constexpr uint32_t KV_BYTES = AtSmem<HD>::KV_BYTES;
     constexpr uint32_t TMEM_COLS = 256;                                     // S: 2 x 64 columns, O: HD columns
@@ -286,6 +287,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int qp = row_ok ? p0 + tok : -1;
         const uint32_t lane_off = (uint32_t)(32 * lane_group) << 16;
         const float sl2 = scale * 1.4426950408889634f;
+        // a bias that grows with the key's distance from the query, slope * (qp - key) off the scaled score: in units of the
+        // raw score here, as everything before the exponential
+        const float slope_raw = (SHAPED && slopes && row_ok) ? slopes[head] / scale : 0.f;
         float m_ref = -INFINITY, l = 0.f;                                              // reference maximum (raw score) and sum
         uint4* p_row = reinterpret_cast<uint4*>(p_tile + (size_t)r * 128);
         bool ok = true;
@@ -300,6 +304,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             at_fence_before();                                                          // this S buffer may be filled again
             __syncwarp();
             if (lane == 0) at_arrive(&s_empty[j & 1]);
+            if (SHAPED && slopes) {                                                     // one fused multiply-add a score
+                const float c0 = -slope_raw * (float)(qp - key0);
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        sv[h][i] = __float_as_uint(fmaf(slope_raw, (float)(32 * h + i), __uint_as_float(sv[h][i]) + c0));
+            }
             // a tile that lies wholly inside what this row may see needs no mask
             const int own = chunk > 0 && qp >= 0 ? (qp / chunk) * chunk : 0;                    // the first key of the row's own chunk
             const bool all_visible = key0 + AT_KEYS - 1 <= qp && key0 + AT_KEYS - 1 < len && (window <= 0 || key0 > qp - window) && key0 >= own;
@@ -374,6 +386,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!ok && lane == 0) atomicExch(error, 5);
         }
         if (ok) {
+            // a sink: one more term of the denominator, exp(sink), relative to the row's reference
+            if (SHAPED && sinks && row_ok) l += at_exp2(sinks[head] * 1.4426950408889634f - (m_ref == -INFINITY ? 0.f : m_ref * sl2));
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = out + ((size_t)(t0 + tok) * Hq + head) * HD;
 #pragma unroll 1
@@ -422,7 +436,7 @@ static AtEncodeFn at_encode() {
 template <int HD>
 static int launch_attn_tc(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
                           const int* pos0, void* out, int B, int T, int max_new, int n_pages, int Hq, int Hkv, int table_width,
-                          float scale, int window, int chunk, int* error, cudaStream_t stream) {
+                          float scale, int window, int chunk, int* error, const float* slopes, const float* sinks, cudaStream_t stream) {
     AtEncodeFn enc = at_encode();
     if (!enc) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: cuTensorMapEncodeTiled is not available from this driver");
     const int G = Hq / Hkv;
@@ -450,22 +464,30 @@ static int launch_attn_tc(const void* q, const void* k_pool, const void* v_pool,
         if (r != CUDA_SUCCESS) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: cuTensorMapEncodeTiled(cache) failed with %d", (int)r);
     }
     const size_t smem = AtSmem<HD>::BYTES;
-    cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const bool shaped = slopes || sinks;
+    cudaError_t e = shaped ? cudaFuncSetAttribute(attn_tc_prefill_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                           : cudaFuncSetAttribute(attn_tc_prefill_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: %s", cudaGetErrorString(e));
     const int tok_per_block = AT_ROWS / G;
     dim3 grid(Hkv, (max_new + tok_per_block - 1) / tok_per_block, B);
-    e = qwb_launch(attn_tc_prefill_kernel<HD>, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, page_table, cu_seqlens, pos0,
-                   (bf16*)out, Hq, Hkv, table_width, scale, window, chunk, G, error);
+    if (shaped)
+        e = qwb_launch(attn_tc_prefill_kernel<HD, true>, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, page_table, cu_seqlens, pos0,
+                       (bf16*)out, Hq, Hkv, table_width, scale, window, chunk, G, error, slopes, sinks);
+    else
+        e = qwb_launch(attn_tc_prefill_kernel<HD, false>, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, page_table, cu_seqlens, pos0,
+                       (bf16*)out, Hq, Hkv, table_width, scale, window, chunk, G, error, slopes, sinks);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: launch failed: %s", cudaGetErrorString(e));
     return qwb_check_launch("attn_tc_prefill");
 }
 
 // bfloat16.  q [T, Hq, hd] with T the packed tokens of all B sequences; pools of n_pages pages; `error` as for qwb_gemm_tc.
 // `chunk` > 0: a query sees the keys of its own block of `chunk` positions only (beside the causal mask and the window).
-extern "C" int qwb_attn_tc_prefill_chunked(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
-                                           const int* cu_seqlens, const int* pos0, void* out, int B, int T, int max_new, int n_pages,
-                                           int Hq, int Hkv, int hd, int page_size, int table_width, float scale, int window,
-                                           int chunk, int* error, cudaStream_t stream) {
+// `slopes` [Hq] (or null): slopes[h] * (query position - key position) is taken off the scaled score; `sinks` [Hq] (or
+// null): exp(sinks[h]) joins the softmax's denominator.
+extern "C" int qwb_attn_tc_prefill_shaped(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                          const int* cu_seqlens, const int* pos0, void* out, int B, int T, int max_new, int n_pages,
+                                          int Hq, int Hkv, int hd, int page_size, int table_width, float scale, int window,
+                                          int chunk, const float* slopes, const float* sinks, int* error, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0 || T <= 0) return 0;
     if (hd != 64 && hd != 128) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: head size %d is not 64 or 128", hd);
     if (page_size != AT_KEYS) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: page size %d is not %d", page_size, AT_KEYS);
@@ -478,8 +500,17 @@ extern "C" int qwb_attn_tc_prefill_chunked(const void* q, const void* k_pool, co
     if (window < 0 || chunk < 0) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: window %d, chunk %d", window, chunk);
     if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16)
         return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: operands must be 16-byte aligned");
-    if (hd == 64) return launch_attn_tc<64>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, chunk, error, stream);
-    return launch_attn_tc<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, chunk, error, stream);
+    if (!(scale > 0.f) && slopes) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: a distance bias needs a positive scale, got %g", (double)scale);
+    if (hd == 64) return launch_attn_tc<64>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, chunk, error, slopes, sinks, stream);
+    return launch_attn_tc<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, chunk, error, slopes, sinks, stream);
+}
+
+extern "C" int qwb_attn_tc_prefill_chunked(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                           const int* cu_seqlens, const int* pos0, void* out, int B, int T, int max_new, int n_pages,
+                                           int Hq, int Hkv, int hd, int page_size, int table_width, float scale, int window,
+                                           int chunk, int* error, cudaStream_t stream) {
+    return qwb_attn_tc_prefill_shaped(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, hd,
+                                      page_size, table_width, scale, window, chunk, nullptr, nullptr, error, stream);
 }
 
 extern "C" int qwb_attn_tc_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table,

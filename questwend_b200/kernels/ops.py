@@ -376,10 +376,12 @@ def tc_attention_fits(dtype: torch.dtype, head_dim: int, page_size: int, group: 
 
 
 def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, scale: float,
-                 window: int = 0, impl: str = "auto", chunk: int = 0) -> torch.Tensor:
+                 window: int = 0, impl: str = "auto", chunk: int = 0, slopes=None, sinks=None) -> torch.Tensor:
     """Causal attention of new tokens over the cache.  q [T, Hq, hd]; returns [T, Hq * hd].
     impl: "auto" (the fastest that fits), "tc" (tcgen05), "mma" (mma.sync), or "plain".  ``chunk`` > 0: a query sees only
-    the keys of its own block of ``chunk`` positions, counted from position 0 (the tcgen05 kernel only)."""
+    the keys of its own block of ``chunk`` positions, counted from position 0; ``slopes`` / ``sinks`` (float32 [Hq]): a
+    bias slopes[h] * distance off the scaled score, and exp(sinks[h]) in the softmax's denominator (all three: the
+    tcgen05 kernel only)."""
     _need(q, "q", k_pool.dtype, 3)
     _need(k_pool, "k_pool", ndim=4)
     _need(v_pool, "v_pool", k_pool.dtype, 4)
@@ -398,13 +400,18 @@ def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, 
     if use_tc:
         if q.dtype != torch.bfloat16:
             raise KernelError("attn_prefill: the tensor-core kernel takes bfloat16 only")
-        _call("attention_tc", "qwb_attn_tc_prefill_chunked", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
+        for name, t in (("slopes", slopes), ("sinks", sinks)):
+            if t is not None:
+                _need(t, name, torch.float32, 1)
+                if t.numel() != Hq:
+                    raise KernelError(f"attn_prefill: {name} of {t.numel()} for {Hq} heads")
+        _call("attention_tc", "qwb_attn_tc_prefill_shaped", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
               _ptr(cu_seqlens), _ptr(pos0), _ptr(out), _i(B), _i(T), _i(max_new), _i(k_pool.shape[0]), _i(Hq),
               _i(k_pool.shape[1]), _i(hd), _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _i(chunk),
-              _ptr(gemm_tc_error_word(q.device)), _stream())
+              _ptr(slopes), _ptr(sinks), _ptr(gemm_tc_error_word(q.device)), _stream())
         return out
-    if chunk:
-        raise KernelError("attn_prefill: only the tcgen05 kernel masks by chunks")
+    if chunk or slopes is not None or sinks is not None:
+        raise KernelError("attn_prefill: only the tcgen05 kernel masks by chunks, biases by distance or has a sink")
     use_mma = impl == "mma" or (impl == "auto" and mma_attention_fits(q.dtype, hd, k_pool.shape[2]))
     if use_mma:
         if q.dtype != torch.bfloat16:
@@ -1308,6 +1315,14 @@ def bias_prep(qkv: torch.Tensor, bias, q_weight, k_weight, cos, sin, ctx, page_t
     return q
 
 
+def bias_tc_fits(q: torch.Tensor, n_kv_heads: int, vdim: int, head_scale, softcap: float, raw: bool) -> bool:
+    """Whether a prompt's attention with shaped scores is what the tcgen05 prompt kernel computes: bfloat16, keys and
+    values of one size that it takes, scores shaped by a distance bias, a window and a sink only."""
+    T, H, dim = q.shape
+    return (head_scale is None and softcap <= 0.0 and not raw and dim == vdim and q.dtype == torch.bfloat16
+            and tc_attention_fits(q.dtype, dim, PAGE_SIZE, H // n_kv_heads))
+
+
 def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: float, head_scale=None, softcap: float = 0.0,
                    slopes=None, window: int = 0, sinks=None, head_mix=None, gate=None, gate_col0: int = 0,
                    impl: str = "auto") -> torch.Tensor:
@@ -1318,8 +1333,9 @@ def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: floa
     the heads' weights are mixed after the softmax, w'_h = sum_g mix[h, g] w_g, each head still reading its own value
     head.  ``gate``: head h's output times sigmoid of column ``gate_col0 + h`` of the float32 matrix ``gate`` [T, ld].
     The per-head vectors are float32 [H].  Steps of one token per sequence take the kernel that cuts the keys into runs
-    (sizes that are multiples of 8); other steps the tensor-core kernel where it fits (``impl`` "auto"; "mma": always),
-    else the plain prompt kernel ("plain")."""
+    (sizes that are multiples of 8); other steps the tensor-core kernels where they fit (``impl`` "auto"; "tc": tcgen05,
+    for scores shaped by a distance bias, a window and a sink only, keys and values of 64 or 128; "mma": mma.sync), else
+    the plain prompt kernel ("plain")."""
     _need(q, "q", k_pool.dtype, 3)
     T, H, dim = q.shape
     G, vdim = k_pool.shape[1], v_pool.shape[3]
@@ -1371,6 +1387,12 @@ def bias_attention(q: torch.Tensor, k_pool, v_pool, page_table, ctx, scale: floa
               _ptr(scratch), _ptr(att), _i(_dt(q.dtype)), _i(1 if raw else 0), _i(T), _i(H), _i(G), _i(1 if all_values else 0),
               _i(dim), _i(vdim), _i(width), _f(scale), _ptr(head_scale), _f(softcap), _ptr(slopes), _i(window), _ptr(sinks),
               _i(n_runs), _stream(), kernels=2)
+    elif (impl in ("auto", "tc") and bias_tc_fits(q, G, vdim, head_scale, softcap, raw)
+          and (impl == "tc" or ctx.max_new * (H // G) >= 64)):
+        # no number per head, no cap, no mix, no gate, keys and values of 64 or 128: plain grouped-query attention whose
+        # softmax takes the distance bias and the sink, on tcgen05
+        return attn_prefill(q, k_pool, v_pool, page_table, ctx.cu_seqlens, ctx.pos0, ctx.max_new, scale, window=window, impl="tc",
+                            slopes=slopes, sinks=sinks)
     elif impl == "mma" or (impl == "auto" and ctx.max_new >= BIAS_MMA_MIN_NEW and bias_prefill_mma_fits(q.dtype, dim, vdim)):
         _call("attention_bias", "qwb_bias_prefill_mma", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
               _ptr(ctx.pos0), _ptr(att), _i(1 if raw else 0), _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G),

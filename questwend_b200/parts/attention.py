@@ -451,7 +451,11 @@ class ShapedScoreAttention(Mixer):
             self.slopes = torch.tensor(slopes, dtype=torch.float32, device=self.w_o.device)
 
     def kernel_modules(self):
-        return ("attention_bias", "rope_kv", *linear_modules(self.runtime.dtype))
+        mods = ["attention_bias", "rope_kv", *linear_modules(self.runtime.dtype)]
+        if (not (self.head_temperature or self.softcap > 0.0 or self.head_mix or self.head_gate) and self.head_dim == self.value_dim
+                and ops.tc_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE, self.n_heads // self.n_kv_heads)):
+            mods.append("attention_tc")         # prompts whose scores a distance bias, a window and a sink shape, keys and values of 64 or 128
+        return tuple(mods)
 
     def kv_spec(self):
         return KVSpec(self.n_kv_heads, self.head_dim, self.window, value_dim=self.value_dim)

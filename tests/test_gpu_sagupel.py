@@ -452,7 +452,7 @@ def shaped_oracle(q, k, v, pos0, scale, head_scale, softcap, slopes, window, sin
 
 @pytest.mark.parametrize("H, G, dim, vdim, window, extras", [
     (4, 2, 64, 64, 0, "cap temp mix gate"), (8, 4, 32, 32, 0, "mix"), (4, 1, 96, 96, 136, "slopes sink"), (2, 2, 16, 24, 70, "slopes sink cap"),
-    (6, 2, 128, 128, 64, "sink"), (3, 1, 48, 8, 1, "slopes"), (2, 1, 256, 256, 0, "gate"), (5, 5, 16, 40, 200, "temp slopes sink mix gate cap")])
+    (6, 2, 128, 128, 64, "sink"), (4, 2, 64, 64, 100, "slopes sink"), (8, 1, 128, 128, 0, "slopes"), (3, 1, 48, 8, 1, "slopes"), (2, 1, 256, 256, 0, "gate"), (5, 5, 16, 40, 200, "temp slopes sink mix gate cap")])
 def test_prompt_kernels_and_the_decode_kernel_against_an_oracle(H, G, dim, vdim, window, extras):
     """Random queries and a random cache: unequal prompts whole and as later portions (queries that start at a position
     above 0, inside a page), and single tokens, on the tensor cores and on the plain kernels."""
@@ -489,6 +489,9 @@ def test_prompt_kernels_and_the_decode_kernel_against_an_oracle(H, G, dim, vdim,
                                    for b, (q, k, v, n0) in enumerate(zip(qs, ks, vs, before))])
             gate = None if gates is None else dev(np.concatenate([np.zeros((sum(counts), 3)), np.concatenate(gates)], axis=1))
             impls = ["auto", "two_pass"] if ctx.single_token else (["plain", "mma"] if dtype == torch.bfloat16 and dim % 16 == 0 else ["plain"])
+            if (not ctx.single_token and dtype == torch.bfloat16 and dim == vdim and dim in (64, 128)
+                    and not any(x in extras for x in ("temp", "cap", "mix", "gate"))):
+                impls.append("tc")                                  # the tcgen05 kernel with the bias and the sink in its softmax
             for impl in impls:
                 # single tokens with mixed heads: the form with all value heads, and the two passes over the keys
                 ops.BIAS_TWO_PASS_FROM_KEYS = 0 if impl == "two_pass" else 10 ** 9
