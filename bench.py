@@ -118,15 +118,15 @@ def sagupel_sizes(width=2048, repeats=2, window=1024, vocab=32768):
     heads = width // 128
     ret = {"type": "retention", "mlp": mlp,
            "mixer": {"decay": [1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)], "dim": 128, "heads": heads, "vdim": 128,
-                     "rot": {"base": 1000000.0, "dims": 128}}}
-    left = {"dim": 128, "heads": heads, "kv_heads": width // 512, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
-            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0}}}
+                     "rot": {"base": 500000.0, "dims": 128}}}
+    left = {"dim": 128, "heads": heads, "kv_heads": width // 512, "vdim": 128, "scale": 128 ** -0.5, "softcap": 25.0,
+            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0}}}
     right = {"conv": 4, "dim": 128, "heads": heads, "kv_heads": width // 512, "vdim": 128}
     pair = {"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right}}
     win = {"type": "attention", "mlp": mlp,
            "mixer": {"dim": 128, "heads": heads, "kv_heads": width // 512, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window}}}
     return {"architecture": "Sagupel", "canon": {"taps": 3}, "layers": [ret, pair, win] * repeats, "norm": {"eps": 1e-5},
-            "postln_alpha": 2.0, "vocab": vocab, "width": width}
+            "postln_alpha": 1.5, "vocab": vocab, "width": width}
 
 
 def qwen3_beside(width=2048, layers=6, vocab=32768):
@@ -727,7 +727,7 @@ def sagupel_kernels(torch, np, peaks) -> dict:
         return p
 
     out = {}
-    H, G, window, cap = 16, 4, 1024, 30.0
+    H, G, window, cap = 16, 4, 1024, 25.0
     slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
     sinks, temp = torch.zeros(H, device=dev), torch.ones(H, device=dev)
     mix = (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, device=dev)).contiguous()

@@ -46,11 +46,11 @@ def parallel(left_m=None, right_m=None):
     return {"type": "parallel", "mixer": {"left": left_m or left(), "right": right_m or right()}}
 
 
-def dense(ff=96, limit=1.5):
+def dense(ff=96, limit=1.25):
     return {"kind": "dense", "ff": ff, "limit": limit}
 
 
-def config(layers, width=64, vocab=96, eps=1e-5, alpha=2.0, taps=3):
+def config(layers, width=64, vocab=96, eps=2e-5, alpha=1.5, taps=4):
     """layers: (mixer entry, mlp entry or None) pairs."""
     out = {"architecture": "Sagupel", "layers": [{**mix, "mlp": mlp} for mix, mlp in layers], "norm": {"eps": eps},
            "vocab": vocab, "width": width}

@@ -295,7 +295,7 @@ def test_delta_rule_with_a_decay_per_head_alone(right, dtype):
 def test_both_mixers_side_by_side_behind_the_input_convolution(dtype):
     entry, width = sh.MIXED["layers"][1], 64
     entry = {"type": entry["type"], "mixer": entry["mixer"]}
-    w = sh.draw_weights(sh.config([(entry, None)], width=width, taps=3), 12)
+    w = sh.draw_weights(sh.config([(entry, None)], width=width, taps=3), 12)      # three taps here, four in the whole models
     rng = np.random.default_rng(13)
     lens, extra = [90, 3], 5
     xs = [f32(rng.standard_normal((n + extra, width))) for n in lens]
@@ -309,7 +309,7 @@ def test_both_mixers_side_by_side_behind_the_input_convolution(dtype):
 
 WINDOWS = [sh.attention(), sh.attention(heads=6, kv_heads=2, dim=8, size=70), sh.attention(heads=3, kv_heads=3, dim=40, size=64, scale=0.2),
            sh.attention(heads=2, kv_heads=1, dim=12, size=5), sh.attention(heads=1, kv_heads=1, dim=8, size=1),
-           sh.attention(heads=4, kv_heads=1, dim=96, size=136, scale=0.12), sh.attention(heads=2, kv_heads=2, dim=16, size=0),
+           sh.attention(heads=4, kv_heads=1, dim=80, size=150, scale=0.12), sh.attention(heads=2, kv_heads=2, dim=16, size=0),
            sh.attention(heads=12, kv_heads=1, dim=32, size=200, scale=0.2)]
 
 
@@ -451,7 +451,7 @@ def shaped_oracle(q, k, v, pos0, scale, head_scale, softcap, slopes, window, sin
 
 
 @pytest.mark.parametrize("H, G, dim, vdim, window, extras", [
-    (4, 2, 64, 64, 0, "cap temp mix gate"), (8, 4, 32, 32, 0, "mix"), (4, 1, 96, 96, 136, "slopes sink"), (2, 2, 16, 24, 70, "slopes sink cap"),
+    (4, 2, 64, 64, 0, "cap temp mix gate"), (8, 4, 32, 32, 0, "mix"), (4, 1, 80, 80, 150, "slopes sink"), (2, 2, 16, 24, 70, "slopes sink cap"),
     (6, 2, 128, 128, 64, "sink"), (4, 2, 64, 64, 100, "slopes sink"), (8, 1, 128, 128, 0, "slopes"), (3, 1, 48, 8, 1, "slopes"), (2, 1, 256, 256, 0, "gate"), (5, 5, 16, 40, 200, "temp slopes sink mix gate cap")])
 def test_prompt_kernels_and_the_decode_kernel_against_an_oracle(H, G, dim, vdim, window, extras):
     """Random queries and a random cache: unequal prompts whole and as later portions (queries that start at a position

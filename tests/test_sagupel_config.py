@@ -15,8 +15,8 @@ from questwend_b200.parts.base import KVSpec, StateSpec
 
 def test_config_reads_every_size_and_round_trips():
     cfg = config_from_dict(sh.MIXED)
-    assert cfg.architecture == "Sagupel" and cfg.width == 64 and cfg.vocab == 96 and cfg.canon_taps == 3
-    assert cfg.postln_alpha == 2.0 and cfg.norm_eps == 1e-5
+    assert cfg.architecture == "Sagupel" and cfg.width == 64 and cfg.vocab == 96 and cfg.canon_taps == 4
+    assert cfg.postln_alpha == 1.5 and cfg.norm_eps == 2e-5
     assert cfg.layers[0]["mixer"]["decay"] == [0.875, 0.96875, 0.9921875] and cfg.layers[2]["mlp"] is None
     assert cfg.layers[1]["mixer"]["left"]["rot"] == {"base": 10000.0, "dims": 8, "scaling": {"factor": 4.0}}
     assert cfg.layers[5]["mixer"]["left"]["rot"] == {"base": 10000.0, "dims": 2} and cfg.layers[5]["mixer"]["left"]["softcap"] == 2.5
@@ -70,7 +70,7 @@ def test_what_the_cache_is_asked_for():
     model = Model(get_architecture("Sagupel").plan(config_from_dict(sh.MIXED)), Runtime(torch.device("cpu"), torch.bfloat16))
     units = model.cache_units()
     assert len(units) == 7
-    tail = StateSpec((2, 64), torch.float32)                    # every layer keeps the last inputs of its input convolution
+    tail = StateSpec((3, 64), torch.float32)                    # every layer keeps the last inputs of its input convolution
     kv, state, cache_of = units[0]
     assert kv is None and state == (tail, StateSpec((3, 8, 16), torch.float32)) and cache_of is None
     kv, state, _ = units[1]
